@@ -1,0 +1,108 @@
+/*
+ * logo_b200 -- C ABI of the B200 (sm_100a) kernels behind the LoGo attention hot path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - The caller owns all memory (inputs, outputs, workspaces); the library never
+ *     allocates, frees or keeps device memory across calls, and never synchronises
+ *     the host with the device. All work is enqueued on `stream`.
+ *   - Token tensors are packed varlen: rows are tokens of all sequences back to back,
+ *     `cu_seqlens[n_seq + 1]` (int32) holds the sequence boundaries.
+ *   - Functions return LOGO_OK (0) or an error code; logo_last_error() gives the text.
+ *     Device-side problems (a bounded wait that expired, an index out of range) are
+ *     reported asynchronously through the caller-provided `status` word (int32,
+ *     device memory, zero-initialised by the caller); 0 = ok.
+ *   - Only head_dim 128 and bf16 activations are supported.
+ *
+ * Each entry point cites the reference interface (Pan-Yuqi/Logo, path:line) it replaces.
+ */
+#ifndef LOGO_B200_H_
+#define LOGO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* logo_stream_t; /* == cudaStream_t */
+
+enum {
+  LOGO_OK = 0,
+  LOGO_ERR_INVALID = 1,     /* bad shape, dtype, alignment or argument            */
+  LOGO_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed                */
+  LOGO_ERR_UNSUPPORTED = 3, /* valid request outside what the kernels implement   */
+  LOGO_ERR_WORKSPACE = 4    /* workspace too small                                */
+};
+
+enum {
+  LOGO_DTYPE_BF16 = 0,
+  LOGO_DTYPE_F32 = 1,
+  LOGO_DTYPE_F16 = 2,
+  LOGO_DTYPE_BOOL = 3 /* one byte per element, non-zero = true */
+};
+
+/* Values a kernel may leave in the device status word. */
+enum {
+  LOGO_DEV_OK = 0,
+  LOGO_DEV_WAIT_TIMEOUT = 1, /* a bounded barrier wait expired; results are invalid */
+  LOGO_DEV_BAD_INDEX = 2,    /* an index derived from q_idx / cu_seqlens was out of range */
+  LOGO_DEV_SCAN_TIMEOUT = 3  /* the prefix-scan look-back gave up                     */
+};
+
+/* Query-tile height of the attention kernels (compacted rows per tile). */
+#define LOGO_TILE 128
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int logo_version(void);
+
+/* Copies the calling thread's last error text into buf (host, NUL-terminated); returns its length. */
+int logo_last_error(char* buf, int n);
+
+/* ------------------------------------------------------------------------------------------
+ * Row selection and compaction.
+ * Replaces logo/ops/common.py:71-107 (build_selection), :110-124 (prepare_chunk_indices) and
+ * the threshold test of logo/layers/logo.py:190, plus the counters of logo/layers/logo.py:251-255.
+ *
+ *   gate        [n_tokens] of gate_dtype (BF16 / F16 / F32: row i is selected iff
+ *               float(gate[i]) >= float(*thres); BOOL: row i is selected iff gate[i] != 0,
+ *               thres is ignored and may be NULL)
+ *   thres       device scalar of thres_dtype (BF16 / F16 / F32)
+ *   cu_seqlens  [n_seq + 1] int32, non-decreasing, cu_seqlens[0] == 0, cu_seqlens[n_seq] == n_tokens
+ * Outputs
+ *   q_idx        [n_tokens] int64; the first Sq entries are the selected token indices, ascending
+ *   pos_ids      [n_tokens] int32; position of each selected token inside its sequence
+ *   cu_seqlens_q [n_seq + 1] int32; prefix sum of selected rows per sequence
+ *   tile_off_q   [n_seq + 1] int32; prefix sum of ceil(selected rows of sequence / 256) (query tile pairs)
+ *   tile_off_k   [n_seq + 1] int32; prefix sum of ceil(sequence length / LOGO_TILE)
+ *   meta         [8] int32: [0] Sq, [1] total query tile pairs, [2] total key tiles,
+ *                [3] number selected (same as Sq), others reserved
+ *   gate_sum     [1] fp32, sum of float(gate) over all rows (0 for BOOL); may be NULL
+ *   workspace    logo_select_workspace_bytes(n_tokens) bytes
+ * ------------------------------------------------------------------------------------------ */
+size_t logo_select_workspace_bytes(int n_tokens);
+
+int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
+                     const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
+                     int32_t* cu_seqlens_q, int32_t* tile_off_q, int32_t* tile_off_k, int32_t* meta,
+                     float* gate_sum, void* workspace, size_t workspace_bytes, int32_t* status,
+                     logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Diagnostics: single-tile tcgen05 matrix multiply used by the GPU test-suite to pin the
+ * shared-memory / tensor-memory operand encodings the attention kernels rely on.
+ * No counterpart in the reference.
+ *   mode 0: C = A * B^T   (A, B both K-major in shared memory)
+ *   mode 1: C = A * B     (B row-major [k][n], i.e. MN-major operand)
+ *   mode 2: C = A * B     (A staged in tensor memory, B MN-major)
+ *   a, b: bf16 [128][128] row-major; c: fp32 [128][128]
+ *   flags bit 0: stage A through thread-written swizzled shared memory instead of TMA.
+ * ------------------------------------------------------------------------------------------ */
+int logo_umma_selftest(int mode, int flags, const void* a, const void* b, float* c, uint32_t lbo_bytes,
+                       uint32_t sbo_bytes, uint32_t kstep_bytes, int32_t* status, logo_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOGO_B200_H_ */

@@ -1,0 +1,41 @@
+// Host-side helpers shared by the C-ABI entry points: error reporting, TMA
+// tensor-map construction through the driver entry point (the library does not
+// link libcuda), per-device immutable properties.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/logo_b200.h"
+
+namespace logo {
+
+// Records a message retrievable through logo_last_error() and returns `code`.
+int set_error(int code, const char* fmt, ...);
+
+#define LOGO_CHECK_CUDA(expr)                                                                      \
+  do {                                                                                             \
+    cudaError_t _e = (expr);                                                                       \
+    if (_e != cudaSuccess)                                                                         \
+      return ::logo::set_error(LOGO_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));   \
+  } while (0)
+
+#define LOGO_REQUIRE(cond, code, ...)                      \
+  do {                                                     \
+    if (!(cond)) return ::logo::set_error(code, __VA_ARGS__); \
+  } while (0)
+
+// 2-D bf16 tensor map with 128-byte swizzle. `inner` elements are contiguous,
+// `outer` rows are `row_stride_bytes` apart. Box = box_inner x box_outer elements;
+// box_inner must be 64 (128 bytes) for the 128-byte swizzle.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace logo
