@@ -74,20 +74,49 @@ int logo_last_error(char* buf, int n);
  *   q_idx        [n_tokens] int64; the first Sq entries are the selected token indices, ascending
  *   pos_ids      [n_tokens] int32; position of each selected token inside its sequence
  *   cu_seqlens_q [n_seq + 1] int32; prefix sum of selected rows per sequence
- *   tile_off_q   [n_seq + 1] int32; prefix sum of ceil(selected rows of sequence / 256) (query tile pairs)
- *   tile_off_k   [n_seq + 1] int32; prefix sum of ceil(sequence length / LOGO_TILE)
- *   meta         [8] int32: [0] Sq, [1] total query tile pairs, [2] total key tiles,
- *                [3] number selected (same as Sq), others reserved
+ *   tile_off     [3][n_seq + 1] int32 work-tile prefix sums consumed by the attention kernels:
+ *                row 0: ceil(selected rows of the sequence / 256)  (query-tile pairs, global branch)
+ *                row 1: ceil(sequence length / 128)                (key tiles, backward)
+ *                row 2: ceil(sequence length / 256)                (query-tile pairs, local branch)
+ *   meta         [8] int32: [0] Sq, [1] total of row 0, [2] total of row 1, [3] total of row 2, rest 0
  *   gate_sum     [1] fp32, sum of float(gate) over all rows (0 for BOOL); may be NULL
- *   workspace    logo_select_workspace_bytes(n_tokens) bytes
+ *   workspace    logo_select_workspace_bytes(n_tokens) bytes, 16-byte aligned
+ * Nothing is copied to the host: Sq stays on the device, so q_idx / pos_ids are sized for n_tokens.
  * ------------------------------------------------------------------------------------------ */
 size_t logo_select_workspace_bytes(int n_tokens);
 
 int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
                      const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
-                     int32_t* cu_seqlens_q, int32_t* tile_off_q, int32_t* tile_off_k, int32_t* meta,
-                     float* gate_sum, void* workspace, size_t workspace_bytes, int32_t* status,
-                     logo_stream_t stream);
+                     int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta, float* gate_sum, void* workspace,
+                     size_t workspace_bytes, int32_t* status, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Query-sparse causal attention, forward (global branch).
+ * Replaces logo/ops/selected_full_attn.py:33-121 (sq_full_attn_fwd_kernel), :340-362 (_fwd) and the
+ * gather / scatter of :461,469-470 (SQFullAttentionFunction.forward).
+ *
+ *   q [n_tokens, hq, 128], k, v [n_tokens, h, 128] bf16, contiguous; hq % h == 0
+ *   q_idx, pos_ids, cu_seqlens_q, tile_off, meta: outputs of logo_select_rows
+ *   o   [n_tokens, hq, 128] bf16: rows listed in q_idx are written; with zero_fill != 0 every other
+ *       row is set to 0 first (the reference returns zeros for unselected rows, :469-471)
+ *   lse [n_tokens, hq] fp32 or NULL: base-2 log-sum-exp of scale * log2(e) * q.k for selected rows
+ *       (the reference keeps it compacted, :118-121; here it is indexed by token)
+ *   scale: softmax scale, > 0 (the reference default is 128 ** -0.5, :523-524)
+ * ------------------------------------------------------------------------------------------ */
+int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int64_t* q_idx,
+                     const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                     const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
+                     float scale, int zero_fill, int32_t* status, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Sliding-window causal attention, forward (local branch): row i attends keys [i - window, i] of
+ * its own sequence. Replaces the flash-attn call of logo/layers/logo.py:166-179 (through
+ * logo/layers/utils.py:157-178 with window_size=(window, window), causal).
+ *   tile_off, meta: outputs of logo_select_rows for the same cu_seqlens (rows 2 / entry 3 are used)
+ * ------------------------------------------------------------------------------------------ */
+int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* cu_seqlens,
+                 const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
+                 int window, float scale, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Diagnostics: single-tile tcgen05 matrix multiply used by the GPU test-suite to pin the

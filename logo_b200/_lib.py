@@ -1,0 +1,95 @@
+"""ctypes binding of ``liblogo_b200.so`` (the C ABI declared in ``include/logo_b200.h``).
+
+There is no fallback: if the shared library is missing or a call fails, an exception is
+raised. Build the library with ``python -m logo_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_uint32, c_void_p
+from pathlib import Path
+from typing import Optional
+
+LIB_PATH = Path(__file__).resolve().parent / "liblogo_b200.so"
+
+DTYPE_BF16, DTYPE_F32, DTYPE_F16, DTYPE_BOOL = 0, 1, 2, 3
+
+DEVICE_STATUS_TEXT = {
+    0: "ok",
+    1: "a bounded barrier wait expired inside a kernel (results invalid)",
+    2: "an index derived from q_idx / cu_seqlens was out of range",
+    3: "the prefix-scan look-back gave up",
+}
+
+# name -> (restype, argtypes); mirrors include/logo_b200.h one to one
+_SIGNATURES = {
+    "logo_version": (c_int, []),
+    "logo_last_error": (c_int, [c_char_p, c_int]),
+    "logo_select_workspace_bytes": (c_size_t, [c_int]),
+    "logo_select_rows": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "logo_sq_attn_fwd": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                                   c_void_p]),
+    "logo_swa_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "logo_umma_selftest": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
+                                   c_void_p, c_void_p]),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def exported_symbols():
+    """Names every build of the library must export (used by the CPU-only ABI test)."""
+    return sorted(_SIGNATURES)
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. "
+            "Run `python -m logo_b200.build` (needs nvcc); there is no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            raise RuntimeError(f"{LIB_PATH} does not export `{name}`; rebuild it with `python -m logo_b200.build`")
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    buf = ctypes.create_string_buffer(512)
+    load().logo_last_error(buf, 512)
+    return buf.value.decode(errors="replace")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (code {rc}): {last_error()}")
+
+
+def ptr(t) -> Optional[int]:
+    """Device pointer of a tensor (None stays NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def torch_dtype_code(dtype) -> int:
+    import torch
+
+    table = {torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32, torch.float16: DTYPE_F16, torch.bool: DTYPE_BOOL}
+    if dtype not in table:
+        raise TypeError(f"unsupported dtype {dtype}")
+    return table[dtype]
+
+
+def current_stream_ptr(device) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream

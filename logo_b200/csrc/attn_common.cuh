@@ -1,0 +1,69 @@
+// Definitions shared by the forward and backward attention kernels: work-item decoding
+// (which sequence / which compacted query rows / which head a CTA works on) and the
+// argument block.
+#pragma once
+
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace logo {
+
+constexpr int HEAD_DIM = 128;   // the only head size the kernels implement
+constexpr int TILE = 128;       // rows of one query tile / keys of one key tile
+constexpr uint32_t BLK_BYTES = 16384;   // one [128][64] bf16 block, 128-byte swizzled
+constexpr uint32_t TILE_BYTES = 32768;  // one [128][128] bf16 tile = two blocks
+
+struct AttnArgs {
+  // activations, bf16, packed tokens
+  const __nv_bfloat16* q;    // [n_tokens, hq, 128]
+  const __nv_bfloat16* k;    // [n_tokens, h, 128]   (device pointer; the kernels read K/V through TMA)
+  const __nv_bfloat16* v;    // [n_tokens, h, 128]
+  __nv_bfloat16* o;          // [n_tokens, hq, 128]
+  float* lse;                // [n_tokens, hq] base-2 log-sum-exp of the scaled scores
+  // backward only
+  const __nv_bfloat16* d_o;  // [n_tokens, hq, 128]
+  float* delta;              // [n_tokens, hq]  sum_d o * do
+  float* dq_acc;             // unused by the two-kernel backward
+  __nv_bfloat16* dq;         // [n_tokens, hq, 128]
+  __nv_bfloat16* dk;         // [n_tokens, h, 128]
+  __nv_bfloat16* dv;         // [n_tokens, h, 128]
+  // selection metadata (q_idx == nullptr: every row is selected, identity mapping)
+  const int64_t* q_idx;      // [Sq] ascending token index of each compacted row
+  const int32_t* pos_ids;    // [Sq] position inside its sequence
+  const int32_t* cu_q;       // [n_seq + 1] compacted-row prefix per sequence
+  const int32_t* cu_k;       // [n_seq + 1] token prefix per sequence
+  const int32_t* tile_off;   // [n_seq + 1] prefix of work tiles per sequence (unit depends on the kernel)
+  const int32_t* n_tiles;    // [1] total number of work tiles
+  int n_seq;
+  int n_tokens;
+  int hq;
+  int h;
+  int window;                // 0: full causal; w > 0: keys [pos - w, pos]
+  float scale_log2;          // softmax scale * log2(e)
+  float scale;               // softmax scale
+  int* status;
+};
+
+// Largest s in [0, n_seq) with off[s] <= x. `off` is a non-decreasing prefix array with off[0] = 0;
+// sequences without tiles (off[s] == off[s+1]) are skipped because the last candidate wins.
+__device__ __forceinline__ int find_sequence(const int32_t* __restrict__ off, int n_seq, int x) {
+  int lo = 0, hi = n_seq;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(off + mid) <= x) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// Position of compacted row `r` (relative to the start of the sequence's compacted rows).
+__device__ __forceinline__ int row_position(const AttnArgs& a, int bos_q, int r) {
+  return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;
+}
+
+// Token index of compacted row `r` of the sequence.
+__device__ __forceinline__ long long row_token(const AttnArgs& a, int bos_q, int bos_k, int r) {
+  return a.q_idx ? (long long)__ldg(a.q_idx + bos_q + r) : (long long)(bos_k + r);
+}
+
+}  // namespace logo

@@ -1,0 +1,527 @@
+// Forward attention for both LoGo branches on tcgen05 tensor cores.
+//
+//   global branch: query-sparse causal attention -- only the rows listed in q_idx are
+//                  computed; K/V of every token of the sequence stay visible;
+//   local branch : every row, keys [pos - window, pos].
+//
+// One CTA works on a pair of query tiles (2 x 128 compacted rows of one sequence and one
+// head). Ten warps:
+//   warps 0-3 / 4-7 : softmax groups for query tile 0 / 1 (one thread per row)
+//   warp 8          : TMA producer, streams 128-key K and V tiles through 2-stage rings
+//   warp 9          : issues tcgen05.mma (one lane)
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each. The bf16
+// probabilities overwrite the first 64 columns of their S buffer and are the A operand of
+// the P*V product straight from tensor memory; V is consumed as an MN-major B operand so
+// the [keys][128] tile is used as it lies in memory.
+// Softmax runs in base 2 with a lazily updated row maximum: the running maximum is only
+// raised (and O rescaled in tensor memory) when a row's new maximum exceeds it by more
+// than 2^8, so most key tiles need no correction pass.
+//
+// Algorithmic work per work item: 4 * 128 * sum over its rows of (visible keys) FLOPs.
+#include "attn_common.cuh"
+#include "host_common.cuh"
+
+namespace logo {
+
+constexpr int FWD_THREADS = 320;
+constexpr int FWD_STAGES = 2;
+constexpr int FWD_SMEM_BYTES = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 1024;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct FwdItem {
+  int hq, kvh, bos_q, bos_k, row0;
+  int nrows[2], min_pos[2], max_pos[2], jb[2], je[2];
+  int JB, JE;
+};
+
+__device__ __forceinline__ void fwd_decode_item(const AttnArgs& a, int w, int total_pairs, FwdItem& it) {
+  const int pair_g = total_pairs - 1 - w / a.hq;
+  it.hq = w % a.hq;
+  it.kvh = it.hq / (a.hq / a.h);
+  const int seq = find_sequence(a.tile_off, a.n_seq, pair_g);
+  const int pair_l = pair_g - __ldg(a.tile_off + seq);
+  it.bos_q = __ldg(a.cu_q + seq);
+  const int nsel = __ldg(a.cu_q + seq + 1) - it.bos_q;
+  it.bos_k = __ldg(a.cu_k + seq);
+  const int len_k = __ldg(a.cu_k + seq + 1) - it.bos_k;
+  it.row0 = pair_l * 2 * TILE;
+  it.JB = 0x7fffffff;
+  it.JE = 0;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = it.row0 + t * TILE;
+    const int n = min(max(nsel - r0, 0), TILE);
+    it.nrows[t] = n;
+    it.min_pos[t] = it.max_pos[t] = 0;
+    it.jb[t] = it.je[t] = 0;
+    if (n > 0) {
+      int lo = row_position(a, it.bos_q, r0);
+      int hi = row_position(a, it.bos_q, r0 + n - 1);
+      if (lo < 0 || hi >= len_k || lo > hi) {  // corrupted metadata: stay inside the sequence
+        if (a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+        lo = max(min(lo, len_k - 1), 0);
+        hi = max(min(hi, len_k - 1), lo);
+      }
+      it.min_pos[t] = lo;
+      it.max_pos[t] = hi;
+      it.je[t] = hi / TILE + 1;
+      it.jb[t] = a.window > 0 ? max(lo - a.window, 0) / TILE : 0;
+      it.JB = min(it.JB, it.jb[t]);
+      it.JE = max(it.JE, it.je[t]);
+    }
+  }
+  if (it.JE == 0) it.JB = 0;
+}
+
+__device__ __forceinline__ bool tile_active(const FwdItem& it, int t, int j) {
+  return it.nrows[t] > 0 && j >= it.jb[t] && j < it.je[t];
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+    attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + 2 * TILE_BYTES;
+  uint8_t* sV = sK + FWD_STAGES * TILE_BYTES;
+
+  __shared__ uint64_t k_full[FWD_STAGES], k_empty[FWD_STAGES], v_full[FWD_STAGES], v_empty[FWD_STAGES];
+  __shared__ uint64_t q_ready[2], s_full[2], p_ready[2], o_done[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  AbortState ab{&abort_flag, a.status};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < FWD_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&q_ready[t], TILE);
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_ready[t], TILE);
+      mbar_init(&o_done[t], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  const int total_pairs = __ldg(a.n_tiles);
+  const long long total_items = (long long)total_pairs * a.hq;
+
+  if (warp < 8) {
+    // =====================================================================================
+    // softmax groups
+    // =====================================================================================
+    const int t = warp >> 2;              // query tile of this group
+    const int row = tid & (TILE - 1);     // row inside the tile == TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + (uint32_t)t * 128u + lane_off;
+    const uint32_t tO = tmem + 256u + (uint32_t)t * 128u + lane_off;
+    uint8_t* sQt = sQ + t * TILE_BYTES;
+    const float c = a.scale_log2;
+    uint32_t n_steps = 0;   // (tile, key-step) pairs processed so far == S / P / O barrier phases
+    uint32_t n_items = 0;   // items in which this tile was active
+
+    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      FwdItem it;
+      fwd_decode_item(a, (int)w, total_pairs, it);
+      const int nrows = it.nrows[t];
+      if (nrows == 0) continue;
+      const int r_base = it.row0 + t * TILE;
+
+      // ---- gather the query rows into swizzled shared memory ----
+      {
+        const int ch = row & 15;  // 16-byte chunk of the 256-byte row
+        uint4 vals[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r = i * 8 + (row >> 4);
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (r < nrows) {
+            const long long tok = row_token(a, it.bos_q, it.bos_k, r_base + r);
+            if (tok >= 0 && tok < a.n_tokens) {
+              v = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.hq + it.hq) * HEAD_DIM) + ch);
+            } else if (a.status) {
+              atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+            }
+          }
+          vals[i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r = i * 8 + (row >> 4);
+          *reinterpret_cast<uint4*>(sQt + (ch >> 3) * BLK_BYTES + sw128_offset((uint32_t)r, (uint32_t)(ch & 7) * 8)) =
+              vals[i];
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&q_ready[t]);
+      ++n_items;
+
+      const int my_r = min(row, nrows - 1);
+      const int my_pos = row_position(a, it.bos_q, r_base + my_r);
+      const int min_pos = it.min_pos[t], max_pos = it.max_pos[t];
+      float m_run = -INFINITY;
+      float l_run = 0.f;
+
+      for (int j = it.jb[t]; j < it.je[t]; ++j) {
+        const bool first = (j == it.jb[t]);
+        const bool masked = (j * TILE + TILE - 1 > min_pos) || (a.window > 0 && j * TILE < max_pos - a.window);
+        const int key_hi = my_pos;                                      // keys <= key_hi are visible
+        const int key_lo = a.window > 0 ? my_pos - a.window : INT32_MIN;  // keys >= key_lo are visible
+
+        mbar_wait(&s_full[t], n_steps & 1u, ab);
+        tc_fence_after();
+
+        // ---- pass 1: row maximum of the raw scores ----
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int chk = 0; chk < 4; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(tS + chk * 32, r);
+          tmem_ld_wait();
+          if (masked) {
+            const int k0 = j * TILE + chk * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = k0 + i;
+              if (key <= key_hi && key >= key_lo) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
+
+        // ---- running maximum, lazy rescale of O ----
+        if (first) {
+          m_run = mx;
+        } else {
+          const float m_new = fmaxf(m_run, mx);
+          const bool need = (m_new > m_run) && ((m_new - m_run) * c > RESCALE_THRESHOLD || m_run == -INFINITY);
+          if (__any_sync(0xffffffffu, need)) {
+            // the previous P*V of this tile must have landed before O is touched
+            mbar_wait(&o_done[t], (n_steps - 1u) & 1u, ab);
+            tc_fence_after();
+            float alpha = 1.f;
+            if (need) {
+              alpha = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * c);
+              m_run = m_new;
+              l_run *= alpha;
+            }
+#pragma unroll 1
+            for (int chk = 0; chk < 4; ++chk) {
+              uint32_t r[32];
+              tmem_ld32(tO + chk * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(tO + chk * 32, r);
+            }
+            tmem_st_wait();
+          }
+        }
+
+        // ---- pass 2: probabilities -> bf16 in tensor memory (over S), row sum ----
+        const float mc = (m_run == -INFINITY) ? 0.f : m_run * c;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll 1
+        for (int chk = 0; chk < 4; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(tS + chk * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+          const int k0 = j * TILE + chk * 32;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float s0 = __uint_as_float(r[2 * i]);
+            float s1 = __uint_as_float(r[2 * i + 1]);
+            if (masked) {
+              const int key0 = k0 + 2 * i, key1 = key0 + 1;
+              if (!(key0 <= key_hi && key0 >= key_lo)) s0 = -INFINITY;
+              if (!(key1 <= key_hi && key1 >= key_lo)) s1 = -INFINITY;
+            }
+            const float p0 = fast_exp2(fmaf(s0, c, -mc));
+            const float p1 = fast_exp2(fmaf(s1, c, -mc));
+            l0 += p0;
+            l1 += p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(tS + chk * 16, pk);
+        }
+        l_run += l0 + l1;
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[t]);
+        ++n_steps;
+      }
+
+      // ---- epilogue: O / l -> bf16 rows of the output, log-sum-exp ----
+      mbar_wait(&o_done[t], (n_steps - 1u) & 1u, ab);
+      tc_fence_after();
+      const bool row_valid = row < nrows;
+      const long long tok = row_valid ? row_token(a, it.bos_q, it.bos_k, r_base + row) : -1;
+      const bool store = row_valid && tok >= 0 && tok < a.n_tokens;
+      const float inv_l = 1.f / l_run;
+      __nv_bfloat16* orow = a.o + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM;
+#pragma unroll 1
+      for (int chk = 0; chk < 4; ++chk) {
+        uint32_t r[32];
+        tmem_ld32(tO + chk * 32, r);
+        tmem_ld_wait();
+        if (store) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + chk * 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv_l, __uint_as_float(r[8 * g + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv_l, __uint_as_float(r[8 * g + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv_l, __uint_as_float(r[8 * g + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv_l, __uint_as_float(r[8 * g + 7]) * inv_l);
+            dst[g] = v;
+          }
+        }
+      }
+      if (store && a.lse) a.lse[(size_t)tok * a.hq + it.hq] = m_run * c + log2f(l_run);
+      tc_fence_before();
+    }
+  } else if (warp == 8) {
+    // =====================================================================================
+    // TMA producer
+    // =====================================================================================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      uint32_t kv_iter = 0;
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        FwdItem it;
+        fwd_decode_item(a, (int)w, total_pairs, it);
+        const int x = it.kvh * HEAD_DIM;
+        for (int j = it.JB; j < it.JE; ++j, ++kv_iter) {
+          const uint32_t st = kv_iter % FWD_STAGES;
+          const uint32_t ph = (kv_iter / FWD_STAGES) & 1u;
+          const int y = it.bos_k + j * TILE;
+          mbar_wait(&k_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+          tma_load_2d(sK + st * TILE_BYTES, &tm_k, &k_full[st], x, y);
+          tma_load_2d(sK + st * TILE_BYTES + BLK_BYTES, &tm_k, &k_full[st], x + 64, y);
+          mbar_wait(&v_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+          tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
+          tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
+        }
+      }
+      // On an aborted run copies may still be in flight: give them a bounded time to land
+      // before the CTA's shared memory is released.
+      if (abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    // =====================================================================================
+    // MMA issuer
+    // =====================================================================================
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc_bf16(TILE, TILE, 0, 0);
+      const uint32_t idesc_pv = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);
+      const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+      uint32_t kv_iter = 0;
+      uint32_t n_p[2] = {0, 0};      // P barriers consumed per tile
+      uint32_t n_items[2] = {0, 0};  // items per tile
+
+      auto issue_s = [&](int t, uint32_t st) {
+        const uint32_t qb = q_base + (uint32_t)t * TILE_BYTES, kb = k_base + st * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
+          umma_ss(tmem + (uint32_t)t * 128u, umma_desc_sw128(qb + off, 0, 1024), umma_desc_sw128(kb + off, 0, 1024),
+                  idesc_qk, kk > 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, uint32_t st, bool acc) {
+        const uint32_t vb = v_base + st * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          umma_ts(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)kk * 8u,
+                  umma_desc_sw128(vb + (uint32_t)kk * 2048u, BLK_BYTES, 1024), idesc_pv, acc || kk > 0);
+        }
+        umma_commit(&o_done[t]);
+      };
+
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        FwdItem it;
+        fwd_decode_item(a, (int)w, total_pairs, it);
+        if (it.JE <= it.JB) continue;
+        for (int t = 0; t < 2; ++t) {
+          if (it.nrows[t] > 0) {
+            mbar_wait(&q_ready[t], n_items[t] & 1u, ab);
+            ++n_items[t];
+          }
+        }
+        tc_fence_after();
+        bool started[2] = {false, false};
+
+        // scores of the first key tile
+        {
+          const uint32_t st = kv_iter % FWD_STAGES, ph = (kv_iter / FWD_STAGES) & 1u;
+          mbar_wait(&k_full[st], ph, ab);
+          tc_fence_after();
+          for (int t = 0; t < 2; ++t)
+            if (tile_active(it, t, it.JB)) issue_s(t, st);
+          umma_commit(&k_empty[st]);
+        }
+        for (int j = it.JB; j < it.JE; ++j, ++kv_iter) {
+          const uint32_t st = kv_iter % FWD_STAGES, ph = (kv_iter / FWD_STAGES) & 1u;
+          const uint32_t st_n = (kv_iter + 1) % FWD_STAGES, ph_n = ((kv_iter + 1) / FWD_STAGES) & 1u;
+          const bool has_next = (j + 1 < it.JE);
+          mbar_wait(&v_full[st], ph, ab);
+          for (int t = 0; t < 2; ++t) {
+            if (tile_active(it, t, j)) {
+              mbar_wait(&p_ready[t], n_p[t] & 1u, ab);
+              ++n_p[t];
+              tc_fence_after();
+              issue_pv(t, st, started[t]);
+              started[t] = true;
+            }
+            if (t == 1) umma_commit(&v_empty[st]);
+            if (has_next) {
+              if (t == 0) {
+                mbar_wait(&k_full[st_n], ph_n, ab);
+                tc_fence_after();
+              }
+              if (tile_active(it, t, j + 1)) issue_s(t, st_n);
+              if (t == 1) umma_commit(&k_empty[st_n]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+static int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
+  CUtensorMap tm_k, tm_v;
+  const uint64_t row_bytes = (uint64_t)a.h * HEAD_DIM * sizeof(__nv_bfloat16);
+  int rc = make_tmap_2d_bf16(&tm_k, a.k, (uint64_t)a.h * HEAD_DIM, (uint64_t)a.n_tokens, row_bytes, 64, TILE);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tm_v, a.v, (uint64_t)a.h * HEAD_DIM, (uint64_t)a.n_tokens, row_bytes, 64, TILE);
+  if (rc) return rc;
+  static thread_local int attr_set_dev = -1;
+  int dev = 0;
+  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (attr_set_dev != dev) {
+    LOGO_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES));
+    attr_set_dev = dev;
+  }
+  const int grid = sm_count();
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tm_k, tm_v, a);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  return LOGO_OK;
+}
+
+static int check_attn_common(const void* q, const void* k, const void* v, const void* o, int n_tokens, int n_seq,
+                             int hq, int h, int d) {
+  LOGO_REQUIRE(d == HEAD_DIM, LOGO_ERR_UNSUPPORTED, "head_dim %d is not supported (only 128)", d);
+  LOGO_REQUIRE(hq > 0 && h > 0 && hq % h == 0, LOGO_ERR_INVALID, "hq (%d) must be a positive multiple of h (%d)", hq, h);
+  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+  LOGO_REQUIRE(n_tokens == 0 || (q && k && v && o), LOGO_ERR_INVALID, "q, k, v and the output must not be NULL");
+  LOGO_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o), LOGO_ERR_INVALID,
+               "q, k, v and the output must be 16-byte aligned");
+  return LOGO_OK;
+}
+
+}  // namespace logo
+
+extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int64_t* q_idx,
+                                const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h,
+                                int d, float scale, int zero_fill, int32_t* status, logo_stream_t stream_) {
+  using namespace logo;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = check_attn_common(q, k, v, o, n_tokens, n_seq, hq, h, d);
+  if (rc) return rc;
+  if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
+  LOGO_REQUIRE(q_idx && pos_ids && cu_seqlens_q && cu_seqlens_k && tile_off && meta, LOGO_ERR_INVALID,
+               "selection metadata pointers must not be NULL");
+  if (zero_fill)
+    LOGO_CHECK_CUDA(cudaMemsetAsync(o, 0, (size_t)n_tokens * hq * HEAD_DIM * sizeof(__nv_bfloat16), stream));
+  AttnArgs a{};
+  a.q = (const __nv_bfloat16*)q;
+  a.k = (const __nv_bfloat16*)k;
+  a.v = (const __nv_bfloat16*)v;
+  a.o = (__nv_bfloat16*)o;
+  a.lse = lse;
+  a.q_idx = q_idx;
+  a.pos_ids = pos_ids;
+  a.cu_q = cu_seqlens_q;
+  a.cu_k = cu_seqlens_k;
+  a.tile_off = tile_off;  // row 0: selected-row pairs
+  a.n_tiles = meta + 1;
+  a.n_seq = n_seq;
+  a.n_tokens = n_tokens;
+  a.hq = hq;
+  a.h = h;
+  a.window = 0;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  return launch_attn_fwd(a, stream);
+}
+
+extern "C" int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                            const int32_t* cu_seqlens, const int32_t* tile_off, const int32_t* meta, int n_seq,
+                            int n_tokens, int hq, int h, int d, int window, float scale, int32_t* status,
+                            logo_stream_t stream_) {
+  using namespace logo;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = check_attn_common(q, k, v, o, n_tokens, n_seq, hq, h, d);
+  if (rc) return rc;
+  LOGO_REQUIRE(window > 0, LOGO_ERR_INVALID, "window must be positive, got %d", window);
+  if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
+  LOGO_REQUIRE(cu_seqlens && tile_off && meta, LOGO_ERR_INVALID, "cu_seqlens, tile_off and meta must not be NULL");
+  AttnArgs a{};
+  a.q = (const __nv_bfloat16*)q;
+  a.k = (const __nv_bfloat16*)k;
+  a.v = (const __nv_bfloat16*)v;
+  a.o = (__nv_bfloat16*)o;
+  a.lse = lse;
+  a.q_idx = nullptr;
+  a.pos_ids = nullptr;
+  a.cu_q = cu_seqlens;
+  a.cu_k = cu_seqlens;
+  a.tile_off = tile_off + 2 * (n_seq + 1);  // row 2: all-row pairs
+  a.n_tiles = meta + 3;
+  a.n_seq = n_seq;
+  a.n_tokens = n_tokens;
+  a.hq = hq;
+  a.h = h;
+  a.window = window;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  return launch_attn_fwd(a, stream);
+}

@@ -1,0 +1,321 @@
+"""Host-side mirror of the reference's ``logo.ops`` package over the sm_100a CUDA library.
+
+Same names, arguments and error behaviour as the reference (``logo/ops/__init__.py:4-23``):
+``sq_full_attn``, ``build_selection``, ``SelInfo``, ``sq_full_attn_dense_ref``,
+``sdpa_causal_ref``, ``get_abs_err``, ``get_err_ratio``, ``assert_close``.
+Everything that computes runs in ``liblogo_b200.so``; there is no Triton, flash-attn or CPU
+path. The ``*_ref`` helpers are the reference's own torch-SDPA checks, kept for API parity.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+__all__ = [
+    "sq_full_attn",
+    "sq_full_attn_dense_ref",
+    "sdpa_causal_ref",
+    "build_selection",
+    "SelInfo",
+    "SelMeta",
+    "select_rows",
+    "swa_attn",
+    "get_abs_err",
+    "get_err_ratio",
+    "assert_close",
+    "check_device_status",
+]
+
+HEAD_DIM = 128
+
+
+# ----------------------------------------------------------------------------------------
+# error metrics (logo/ops/common.py:24-41)
+# ----------------------------------------------------------------------------------------
+def get_abs_err(x, y):
+    return (x.detach() - y.detach()).flatten().abs().max().item()
+
+
+def get_err_ratio(x, y):
+    err = (x.detach() - y.detach()).flatten().square().mean().sqrt().item()
+    base = (x.detach()).flatten().square().mean().sqrt().item()
+    return err / (base + 1e-8)
+
+
+def assert_close(prefix, ref, tri, ratio, err_atol=1e-6):
+    abs_atol = get_abs_err(ref, tri)
+    msg = f"{prefix} diff: {abs_atol:.6e} ratio: {get_err_ratio(ref, tri):.6e}"
+    error_rate = get_err_ratio(ref, tri)
+    if abs_atol <= err_atol:
+        return msg
+    assert error_rate < ratio, msg
+    return msg
+
+
+# ----------------------------------------------------------------------------------------
+# selection metadata
+# ----------------------------------------------------------------------------------------
+@dataclass
+class SelInfo:
+    """Same fields as the reference's SelInfo (logo/ops/common.py:44-68)."""
+
+    q_idx: torch.Tensor
+    pos_ids: torch.Tensor
+    cu_seqlens_q: torch.Tensor
+    cu_seqlens_k: torch.Tensor
+    B: int
+    T: int
+    Nseq: int
+    Sq: int
+
+
+@dataclass
+class SelMeta:
+    """Device-resident output of the select kernel; nothing here has been copied to the host.
+
+    ``q_idx`` / ``pos_ids`` are sized for every token; only the first ``meta[0]`` entries are valid.
+    """
+
+    q_idx: torch.Tensor          # int64 [N]
+    pos_ids: torch.Tensor        # int32 [N]
+    cu_seqlens_q: torch.Tensor   # int32 [Nseq+1]
+    cu_seqlens_k: torch.Tensor   # int32 [Nseq+1]
+    tile_off: torch.Tensor       # int32 [3, Nseq+1]
+    meta: torch.Tensor           # int32 [8]
+    gate_sum: torch.Tensor       # fp32 [1]
+    status: torch.Tensor         # int32 [1] device status word shared by the kernels using this metadata
+    n_tokens: int
+    n_seq: int
+
+
+def check_device_status(status: torch.Tensor, what: str = "logo_b200 kernels") -> None:
+    """Reads the device status word (this synchronises) and raises if a kernel reported a problem."""
+    code = int(status.item())
+    if code != 0:
+        raise RuntimeError(f"{what}: device status {code}: {_lib.DEVICE_STATUS_TEXT.get(code, 'unknown')}")
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("logo_b200 operators run on CUDA tensors only; there is no CPU fallback")
+
+
+def select_rows(gate_or_mask: torch.Tensor, thres: Optional[torch.Tensor], cu_seqlens: torch.Tensor) -> SelMeta:
+    """Runs the select / compact kernel. ``gate_or_mask`` is a flat ``[N]`` float gate (compared
+    ``>= thres`` in fp32, ``thres`` a one-element device tensor) or a bool mask."""
+    _require_cuda(gate_or_mask, cu_seqlens, thres)
+    lib = _lib.load()
+    flat = gate_or_mask.reshape(-1).contiguous()
+    dev = flat.device
+    n = flat.numel()
+    cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+    nseq = cu.numel() - 1
+    q_idx = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    pos_ids = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    cu_q = torch.empty(nseq + 1, dtype=torch.int32, device=dev)
+    tile_off = torch.empty(3, nseq + 1, dtype=torch.int32, device=dev)
+    meta = torch.empty(8, dtype=torch.int32, device=dev)
+    gate_sum = torch.empty(1, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws_bytes = lib.logo_select_workspace_bytes(n)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    if flat.dtype == torch.bool:
+        thres_ptr, thres_code = None, _lib.DTYPE_F32
+    else:
+        if thres is None:
+            raise ValueError("a floating-point gate needs a threshold tensor")
+        thres = thres.reshape(-1)[:1].contiguous()
+        thres_ptr, thres_code = thres.data_ptr(), _lib.torch_dtype_code(thres.dtype)
+    rc = lib.logo_select_rows(flat.data_ptr(), _lib.torch_dtype_code(flat.dtype), thres_ptr, thres_code,
+                              cu.data_ptr(), nseq, n, q_idx.data_ptr(), pos_ids.data_ptr(), cu_q.data_ptr(),
+                              tile_off.data_ptr(), meta.data_ptr(), gate_sum.data_ptr(), ws.data_ptr(), ws_bytes,
+                              status.data_ptr(), _lib.current_stream_ptr(dev))
+    _lib.check(rc, "logo_select_rows")
+    return SelMeta(q_idx, pos_ids, cu_q, cu, tile_off, meta, gate_sum, status, n, nseq)
+
+
+def build_selection(selection: torch.Tensor, B: int, T: int, cu_seqlens: Optional[torch.Tensor] = None) -> SelInfo:
+    """Selection metadata for packed variable-length input (logo/ops/common.py:71-107).
+
+    Like the reference, this public helper returns a python ``Sq`` and therefore synchronises;
+    ``sq_full_attn`` itself goes through :func:`select_rows` and does not.
+    """
+    m = select_rows(selection.reshape(-1), None, cu_seqlens)
+    sq = int(m.meta[0].item())
+    check_device_status(m.status, "build_selection")
+    return SelInfo(q_idx=m.q_idx[:sq], pos_ids=m.pos_ids[:sq], cu_seqlens_q=m.cu_seqlens_q,
+                   cu_seqlens_k=m.cu_seqlens_k, B=B, T=T, Nseq=m.n_seq, Sq=sq)
+
+
+# ----------------------------------------------------------------------------------------
+# raw kernel launchers (no autograd)
+# ----------------------------------------------------------------------------------------
+def _check_qkv(q, k, v):
+    _require_cuda(q, k, v)
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("logo_b200 attention kernels take bf16 q/k/v")
+    if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM or v.shape[-1] != HEAD_DIM:
+        raise NotImplementedError(f"only head_dim {HEAD_DIM} is implemented")
+
+
+def sq_attn_fwd_raw(q, k, v, m: SelMeta, scale: float, zero_fill: bool = True):
+    """q [N,HQ,D], k/v [N,H,D] contiguous bf16 -> (o [N,HQ,D], lse [N,HQ])."""
+    _check_qkv(q, k, v)
+    lib = _lib.load()
+    n, hq, d = q.shape
+    h = k.shape[1]
+    o = torch.empty_like(q)
+    lse = torch.empty(n, hq, dtype=torch.float32, device=q.device)
+    rc = lib.logo_sq_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                              m.q_idx.data_ptr(), m.pos_ids.data_ptr(), m.cu_seqlens_q.data_ptr(),
+                              m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h,
+                              d, float(scale), int(zero_fill), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
+    _lib.check(rc, "logo_sq_attn_fwd")
+    return o, lse
+
+
+def swa_fwd_raw(q, k, v, m: SelMeta, window: int, scale: float):
+    """Local-branch forward on packed tokens: (o [N,HQ,D], lse [N,HQ])."""
+    _check_qkv(q, k, v)
+    lib = _lib.load()
+    n, hq, d = q.shape
+    h = k.shape[1]
+    o = torch.empty_like(q)
+    lse = torch.empty(n, hq, dtype=torch.float32, device=q.device)
+    rc = lib.logo_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                          m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h, d,
+                          int(window), float(scale), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
+    _lib.check(rc, "logo_swa_fwd")
+    return o, lse
+
+
+# ----------------------------------------------------------------------------------------
+# autograd functions
+# ----------------------------------------------------------------------------------------
+class SQFullAttentionFunction(torch.autograd.Function):
+    """Counterpart of logo/ops/selected_full_attn.py:449-492 (same argument order)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, sel: SelMeta):
+        B, T, HQ, K = q.shape
+        H, V = v.shape[2], v.shape[3]
+        qf = q.contiguous().reshape(B * T, HQ, K)
+        kf = k.contiguous().reshape(B * T, H, K)
+        vf = v.contiguous().reshape(B * T, H, V)
+        o, lse = sq_attn_fwd_raw(qf, kf, vf, sel, scale, zero_fill=True)
+        ctx.save_for_backward(qf, kf, vf, o, lse)
+        ctx.sel = sel
+        ctx.scale = scale
+        ctx.shapes = (B, T, HQ, H, K, V)
+        return o.view(B, T, HQ, V)
+
+    @staticmethod
+    def backward(ctx, do):
+        from .ops_bwd import sq_attn_bwd_raw
+
+        qf, kf, vf, o, lse = ctx.saved_tensors
+        B, T, HQ, H, K, V = ctx.shapes
+        dof = do.contiguous().reshape(B * T, HQ, V)
+        dq, dk, dv = sq_attn_bwd_raw(qf, kf, vf, o, lse, dof, ctx.sel, ctx.scale)
+        return dq.view(B, T, HQ, K), dk.view(B, T, H, K), dv.view(B, T, H, V), None, None
+
+
+class SWAFunction(torch.autograd.Function):
+    """Local sliding-window branch (the flash-attn call of logo/layers/logo.py:166-179)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, window, scale, sel: SelMeta):
+        qf, kf, vf = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = swa_fwd_raw(qf, kf, vf, sel, window, scale)
+        ctx.save_for_backward(qf, kf, vf, o, lse)
+        ctx.sel, ctx.window, ctx.scale = sel, window, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from .ops_bwd import swa_bwd_raw
+
+        qf, kf, vf, o, lse = ctx.saved_tensors
+        dq, dk, dv = swa_bwd_raw(qf, kf, vf, o, lse, do.contiguous(), ctx.sel, ctx.window, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
+def swa_attn(q, k, v, cu_seqlens, window: int, scale: Optional[float] = None, sel: Optional[SelMeta] = None):
+    """Sliding-window causal attention on packed tokens ``[N, H, D]`` (keys ``[i-window, i]``)."""
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if sel is None:
+        sel = select_rows(torch.ones(q.shape[0], dtype=torch.bool, device=q.device), None, cu_seqlens)
+    return SWAFunction.apply(q, k, v, window, scale, sel)
+
+
+def sq_full_attn(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    selection: torch.Tensor,
+    scale: Optional[float] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    r"""Selected-query full causal attention (logo/ops/selected_full_attn.py:495-527).
+
+    Args:
+        q: queries `[1, total_tokens, HQ, K]`.
+        k: keys    `[1, total_tokens, H, K]` (GQA when HQ % H == 0).
+        v: values  `[1, total_tokens, H, V]`.
+        selection: per-token bool mask `[1, total_tokens]`.
+        scale: attention scale; defaults to `K ** -0.5`.
+        cu_seqlens: required `[Nseq+1]` int tensor for packed varlen input.
+
+    Returns:
+        o: `[1, total_tokens, HQ, V]`; rows for unselected query tokens are 0.
+    """
+    B, T, HQ, K = q.shape
+    H = k.shape[2]
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q/k/v must be [B, T, H, D]"
+    assert HQ % H == 0, "HQ must be a multiple of H (GQA)"
+    assert selection.dtype == torch.bool and selection.shape == (B, T), "selection must be a bool mask [B, T]"
+    assert B == 1, "sq_full_attn only supports B=1 packed-varlen input"
+    assert cu_seqlens is not None, "sq_full_attn requires explicit cu_seqlens"
+    if scale is None:
+        scale = K ** -0.5
+    sel = select_rows(selection.reshape(-1), None, cu_seqlens)
+    return SQFullAttentionFunction.apply(q, k, v, scale, sel)
+
+
+# ----------------------------------------------------------------------------------------
+# the reference's dense checks (logo/ops/dense_full_attn.py), kept for API parity
+# ----------------------------------------------------------------------------------------
+def sq_full_attn_dense_ref(q, k, v, scale=None, cu_seqlens=None):
+    """Full causal attention through the shared kernels (selection = all ones), dense_full_attn.py:12-22."""
+    B, T, HQ, K = q.shape
+    selection = torch.ones(B, T, dtype=torch.bool, device=q.device)
+    return sq_full_attn(q, k, v, selection, scale=scale, cu_seqlens=cu_seqlens)
+
+
+def sdpa_causal_ref(q, k, v, scale=None, cu_seqlens=None):
+    """Independent causal-attention check with torch SDPA (dense_full_attn.py:30-69)."""
+    B, T, HQ, K = q.shape
+    H = k.shape[2]
+    G = HQ // H
+    if scale is None:
+        scale = K ** -0.5
+
+    def rep(x):
+        b, t, h, d = x.shape
+        return x[:, :, :, None, :].expand(b, t, h, G, d).reshape(b, t, h * G, d)
+
+    qh, kh, vh = q.transpose(1, 2), rep(k).transpose(1, 2), rep(v).transpose(1, 2)
+    if cu_seqlens is None:
+        return F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale).transpose(1, 2).contiguous()
+    assert B == 1
+    cu = cu_seqlens.tolist()
+    outs = [F.scaled_dot_product_attention(qh[:, :, a:b], kh[:, :, a:b], vh[:, :, a:b], is_causal=True, scale=scale)
+            for a, b in zip(cu[:-1], cu[1:])]
+    return torch.cat(outs, dim=2).transpose(1, 2).contiguous()
