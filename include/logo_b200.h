@@ -74,11 +74,12 @@ int logo_last_error(char* buf, int n);
  *   q_idx        [n_tokens] int64; the first Sq entries are the selected token indices, ascending
  *   pos_ids      [n_tokens] int32; position of each selected token inside its sequence
  *   cu_seqlens_q [n_seq + 1] int32; prefix sum of selected rows per sequence
- *   tile_off     [3][n_seq + 1] int32 work-tile prefix sums consumed by the attention kernels:
+ *   tile_off     [4][n_seq + 1] int32 work-tile prefix sums consumed by the attention kernels:
  *                row 0: ceil(selected rows of the sequence / 256)  (query-tile pairs, global branch)
  *                row 1: ceil(sequence length / 128)                (key tiles, backward)
  *                row 2: ceil(sequence length / 256)                (query-tile pairs, local branch)
- *   meta         [8] int32: [0] Sq, [1] total of row 0, [2] total of row 1, [3] total of row 2, rest 0
+ *                row 3: ceil(selected rows of the sequence / 128)  (query tiles, backward)
+ *   meta         [8] int32: [0] Sq, [1..4] totals of rows 0..3, rest 0
  *   gate_sum     [1] fp32, sum of float(gate) over all rows (0 for BOOL); may be NULL
  *   workspace    logo_select_workspace_bytes(n_tokens) bytes, 16-byte aligned
  * Nothing is copied to the host: Sq stays on the device, so q_idx / pos_ids are sized for n_tokens.
@@ -117,6 +118,34 @@ int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float
 int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* cu_seqlens,
                  const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
                  int window, float scale, int32_t* status, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Backward of both attention branches.
+ * logo_sq_attn_bwd replaces logo/ops/selected_full_attn.py:124-138 (delta), :141-228 (dQ),
+ * :231-337 (dK/dV), :374-402 (_compute_q_start_blk), :405-446 (_bwd incl. the GQA reduction of
+ * :444-445) and the gather / scatter / casts of :483-491 (SQFullAttentionFunction.backward).
+ * logo_swa_bwd is the backward of the flash-attn call of logo/layers/logo.py:166-179.
+ *
+ *   q, k, v, o, lse: as given to / produced by the matching forward call
+ *   d_o [n_tokens, hq, 128] bf16: gradient of o (rows of unselected tokens are ignored)
+ *   dq  [n_tokens, hq, 128] bf16: fully written (zeros on unselected rows, :487-488)
+ *   dk, dv [n_tokens, h, 128] bf16: fully written
+ *   workspace: logo_attn_bwd_workspace_bytes(n_tokens, hq, gathered) bytes, 256-byte aligned;
+ *              gathered = 1 for logo_sq_attn_bwd (packed copies of the selected Q / dO rows,
+ *              head-major lse and delta), 0 for logo_swa_bwd (lse and delta only)
+ * ------------------------------------------------------------------------------------------ */
+size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered);
+
+int logo_sq_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                     void* dq, void* dk, void* dv, const int64_t* q_idx, const int32_t* pos_ids,
+                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* tile_off,
+                     const int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq,
+                     int h, int d, float scale, int32_t* status, logo_stream_t stream);
+
+int logo_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                 void* dq, void* dk, void* dv, const int32_t* cu_seqlens, const int32_t* tile_off,
+                 const int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq, int h,
+                 int d, int window, float scale, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Diagnostics: single-tile tcgen05 matrix multiply used by the GPU test-suite to pin the

@@ -31,6 +31,11 @@ _SIGNATURES = {
     "logo_sq_attn_fwd": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                                    c_void_p]),
     "logo_swa_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "logo_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "logo_sq_attn_bwd": (c_int, [c_void_p] * 16 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                                   c_void_p]),
+    "logo_swa_bwd": (c_int, [c_void_p] * 13 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                               c_void_p]),
     "logo_umma_selftest": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
                                    c_void_p, c_void_p]),
 }

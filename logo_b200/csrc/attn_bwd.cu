@@ -1,0 +1,942 @@
+// Backward attention for both LoGo branches on tcgen05 tensor cores.
+//
+// Three kernels:
+//   1. bwd_preprocess_kernel: delta = sum_d o * dO per (row, head); for the query-sparse
+//      branch it also packs the selected rows of Q and dO into contiguous buffers so the
+//      two GEMM kernels can stream them with TMA, and transposes lse to head-major.
+//   2. attn_bwd_dq_kernel: one CTA per (128-row query tile, head); streams K/V tiles.
+//        S = Q K^T, dP = dO V^T, dS = P o (dP - delta), dQ += dS K
+//   3. attn_bwd_dkv_kernel: one CTA per (128-key tile, kv head); streams Q/dO tiles of every
+//      query head of the group (the GQA reduction happens in the accumulators).
+//        S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q
+// In both GEMM kernels warps 0-7 do the element-wise work: warp w owns TMEM lanes
+// 32*(w%4).. and the 64 columns starting at 64*(w/4) of each 128x128 tile; warp 8 is the
+// TMA producer and warp 9 issues the MMAs. P / dS are written back to tensor memory as
+// bf16 over the S / dP accumulators and consumed as the A operand of the next product;
+// the tile that supplies the B operand of that product ([rows][128] as it lies in memory)
+// is read through an MN-major descriptor.
+//
+// Algorithmic work: 2.5x the forward FLOPs (5 products against 2); S is recomputed in both
+// GEMM kernels, so 7 products execute.
+#include "attn_common.cuh"
+#include "host_common.cuh"
+
+namespace logo {
+
+struct BwdArgs {
+  const int64_t* q_idx;       // null: identity (local branch)
+  const int32_t* pos_ids;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  const int32_t* tile_off_q;  // [n_seq+1] prefix of 128-row query tiles
+  const int32_t* n_qtiles;
+  const int32_t* tile_off_k;  // [n_seq+1] prefix of 128-key tiles
+  const int32_t* n_ktiles;
+  const float* lse_sel;       // [hq][cap] head-major, compact rows
+  const float* delta_sel;     // [hq][cap]
+  int cap;
+  __nv_bfloat16* dq;          // [n_tokens, hq, 128]
+  __nv_bfloat16* dk;          // [n_tokens, h, 128]
+  __nv_bfloat16* dv;
+  int n_seq, n_tokens, hq, h, window;
+  float scale, scale_log2;
+  int* status;
+};
+
+constexpr int BWD_THREADS = 320;
+constexpr int BWD_SMEM_BYTES = 6 * TILE_BYTES + 1024;
+
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ int bwd_row_position(const BwdArgs& a, int bos_q, int r) {
+  return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;
+}
+
+// ---------------------------------------------------------------------------------------
+// 1. preprocess
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+    bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ o,
+                          const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
+                          const int64_t* __restrict__ q_idx, const int32_t* __restrict__ sq_ptr,
+                          __nv_bfloat16* __restrict__ q_sel, __nv_bfloat16* __restrict__ do_sel,
+                          float* __restrict__ lse_sel, float* __restrict__ delta_sel, int cap, int n_tokens, int hq,
+                          int* status) {
+  const bool gathered = (q_idx != nullptr);
+  const int sq = gathered ? min(max(__ldg(sq_ptr), 0), n_tokens) : n_tokens;
+  const int rows_total = gathered ? min(sq + TILE, cap) : sq;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < rows_total; r += gridDim.x * warps_per_block) {
+    if (r < sq) {
+      long long tok = gathered ? __ldg(q_idx + r) : (long long)r;
+      if (tok < 0 || tok >= n_tokens) {
+        if (lane == 0 && status) atomicCAS(status, 0, (int)DEV_BAD_INDEX);
+        tok = 0;
+      }
+      for (int hh = 0; hh < hq; ++hh) {
+        const size_t src = ((size_t)tok * hq + hh) * HEAD_DIM + lane * 4;
+        const uint2 ov = __ldg(reinterpret_cast<const uint2*>(o + src));
+        const uint2 dv = __ldg(reinterpret_cast<const uint2*>(d_o + src));
+        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float2 of = __bfloat1622float2(o2[i]);
+          const float2 df = __bfloat1622float2(d2[i]);
+          acc = fmaf(of.x, df.x, acc);
+          acc = fmaf(of.y, df.y, acc);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+          delta_sel[(size_t)hh * cap + r] = acc;
+          lse_sel[(size_t)hh * cap + r] = __ldg(lse + (size_t)tok * hq + hh);
+        }
+        if (gathered) {
+          const size_t dst = ((size_t)r * hq + hh) * HEAD_DIM + lane * 4;
+          *reinterpret_cast<uint2*>(q_sel + dst) = __ldg(reinterpret_cast<const uint2*>(q + src));
+          *reinterpret_cast<uint2*>(do_sel + dst) = dv;
+        }
+      }
+    } else {
+      // padding rows behind the last selected row: tiles may read them, keep them finite
+      for (int hh = 0; hh < hq; ++hh) {
+        const size_t dst = ((size_t)r * hq + hh) * HEAD_DIM + lane * 4;
+        *reinterpret_cast<uint2*>(q_sel + dst) = make_uint2(0, 0);
+        *reinterpret_cast<uint2*>(do_sel + dst) = make_uint2(0, 0);
+        if (lane == 0) {
+          delta_sel[(size_t)hh * cap + r] = 0.f;
+          lse_sel[(size_t)hh * cap + r] = 0.f;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// 2. dQ
+// ---------------------------------------------------------------------------------------
+struct DqItem {
+  int hq, kvh, bos_q, bos_k, r_base, nrows, min_pos, max_pos, jb, je;
+};
+
+__device__ __forceinline__ void dq_decode_item(const BwdArgs& a, int w, int total_tiles, DqItem& it) {
+  const int tile_g = total_tiles - 1 - w / a.hq;
+  it.hq = w % a.hq;
+  it.kvh = it.hq / (a.hq / a.h);
+  const int seq = find_sequence(a.tile_off_q, a.n_seq, tile_g);
+  const int tile_l = tile_g - __ldg(a.tile_off_q + seq);
+  it.bos_q = __ldg(a.cu_q + seq);
+  const int nsel = __ldg(a.cu_q + seq + 1) - it.bos_q;
+  it.bos_k = __ldg(a.cu_k + seq);
+  const int len_k = __ldg(a.cu_k + seq + 1) - it.bos_k;
+  it.r_base = tile_l * TILE;
+  it.nrows = min(max(nsel - it.r_base, 0), TILE);
+  it.min_pos = it.max_pos = 0;
+  it.jb = it.je = 0;
+  if (it.nrows > 0) {
+    int lo = bwd_row_position(a, it.bos_q, it.r_base);
+    int hi = bwd_row_position(a, it.bos_q, it.r_base + it.nrows - 1);
+    if (lo < 0 || hi >= len_k || lo > hi) {
+      if (a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+      lo = max(min(lo, len_k - 1), 0);
+      hi = max(min(hi, len_k - 1), lo);
+    }
+    it.min_pos = lo;
+    it.max_pos = hi;
+    it.je = hi / TILE + 1;
+    it.jb = a.window > 0 ? max(lo - a.window, 0) / TILE : 0;
+  }
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const BwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* sV = smem + 4 * TILE_BYTES;   // 2 stages
+
+  __shared__ uint64_t qdo_full, qdo_free, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ uint64_t s_full[2], dp_full, ds_ready, acc_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  AbortState ab{&abort_flag, a.status};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&qdo_full, 1);
+    mbar_init(&qdo_free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
+    mbar_init(&dp_full, 1);
+    mbar_init(&ds_ready, 256);
+    mbar_init(&acc_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t TM_S = tmem, TM_DP = tmem + 256u, TM_DQ = tmem + 384u;
+
+  const int total_tiles = __ldg(a.n_qtiles);
+  const long long total_items = (long long)total_tiles * a.hq;
+
+  if (warp < 8) {
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int col0 = half * 64;
+    const float c = a.scale_log2;
+    uint32_t idx = 0;      // key steps processed so far (all items)
+    uint32_t n_items = 0;
+
+    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      DqItem it;
+      dq_decode_item(a, (int)w, total_tiles, it);
+      if (it.nrows == 0) continue;
+      const int rowv = min(row, it.nrows - 1);
+      const int my_pos = bwd_row_position(a, it.bos_q, it.r_base + rowv);
+      const size_t sidx = (size_t)it.hq * a.cap + it.bos_q + it.r_base + rowv;
+      const float lse_r = __ldg(a.lse_sel + sidx);
+      const float delta_r = __ldg(a.delta_sel + sidx);
+      const int key_hi = my_pos;
+      const int key_lo = a.window > 0 ? my_pos - a.window : INT32_MIN;
+
+      for (int j = it.jb; j < it.je; ++j, ++idx) {
+        const bool masked =
+            (j * TILE + TILE - 1 > it.min_pos) || (a.window > 0 && j * TILE < it.max_pos - a.window);
+        const uint32_t tS = TM_S + (idx & 1u) * 128u + lane_off + (uint32_t)col0;
+        float p[64];
+        mbar_wait(&s_full[idx & 1u], (idx >> 1) & 1u, ab);
+        tc_fence_after();
+#pragma unroll
+        for (int chk = 0; chk < 2; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(tS + chk * 32, r);
+          tmem_ld_wait();
+          const int k0 = j * TILE + col0 + chk * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float pv = fast_exp2(fmaf(__uint_as_float(r[i]), c, -lse_r));
+            if (masked) {
+              const int key = k0 + i;
+              if (!(key <= key_hi && key >= key_lo)) pv = 0.f;
+            }
+            p[chk * 32 + i] = pv;
+          }
+        }
+        mbar_wait(&dp_full, idx & 1u, ab);
+        tc_fence_after();
+        uint32_t pk[32];
+#pragma unroll
+        for (int chk = 0; chk < 2; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(TM_DP + lane_off + (uint32_t)col0 + chk * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float d0 = p[chk * 32 + 2 * i] * (__uint_as_float(r[2 * i]) - delta_r);
+            const float d1 = p[chk * 32 + 2 * i + 1] * (__uint_as_float(r[2 * i + 1]) - delta_r);
+            pk[chk * 16 + i] = pack_bf16x2(d0, d1);
+          }
+        }
+        // every warp has finished reading dP before anyone overwrites it with dS
+        named_barrier_sync(1, 256);
+        tmem_st32(TM_DP + lane_off + (uint32_t)(half * 32), pk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&ds_ready);
+      }
+
+      // ---- epilogue: dQ * scale -> bf16 rows ----
+      mbar_wait(&acc_done, n_items & 1u, ab);
+      tc_fence_after();
+      ++n_items;
+      long long tok = -1;
+      if (row < it.nrows)
+        tok = a.q_idx ? __ldg(a.q_idx + it.bos_q + it.r_base + row) : (long long)(it.bos_k + it.r_base + row);
+      const bool store = tok >= 0 && tok < a.n_tokens;
+      __nv_bfloat16* dst_row = a.dq + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM + col0;
+#pragma unroll
+      for (int chk = 0; chk < 2; ++chk) {
+        uint32_t r[32];
+        tmem_ld32(TM_DQ + lane_off + (uint32_t)col0 + chk * 32, r);
+        tmem_ld_wait();
+        if (store) {
+          uint4* dst = reinterpret_cast<uint4*>(dst_row + chk * 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * a.scale, __uint_as_float(r[8 * g + 1]) * a.scale);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * a.scale, __uint_as_float(r[8 * g + 3]) * a.scale);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * a.scale, __uint_as_float(r[8 * g + 5]) * a.scale);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * a.scale, __uint_as_float(r[8 * g + 7]) * a.scale);
+            dst[g] = v;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      uint32_t kv_iter = 0, n_items = 0;
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        DqItem it;
+        dq_decode_item(a, (int)w, total_tiles, it);
+        if (it.nrows == 0) continue;
+        const int xq = it.hq * HEAD_DIM, yq = it.bos_q + it.r_base;
+        mbar_wait(&qdo_free, (n_items & 1u) ^ 1u, ab);
+        mbar_arrive_expect_tx(&qdo_full, 2 * TILE_BYTES);
+        tma_load_2d(sQ, &tm_q, &qdo_full, xq, yq);
+        tma_load_2d(sQ + BLK_BYTES, &tm_q, &qdo_full, xq + 64, yq);
+        tma_load_2d(sDO, &tm_do, &qdo_full, xq, yq);
+        tma_load_2d(sDO + BLK_BYTES, &tm_do, &qdo_full, xq + 64, yq);
+        ++n_items;
+        const int x = it.kvh * HEAD_DIM;
+        for (int j = it.jb; j < it.je; ++j, ++kv_iter) {
+          const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
+          const int y = it.bos_k + j * TILE;
+          mbar_wait(&k_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+          tma_load_2d(sK + st * TILE_BYTES, &tm_k, &k_full[st], x, y);
+          tma_load_2d(sK + st * TILE_BYTES + BLK_BYTES, &tm_k, &k_full[st], x + 64, y);
+          mbar_wait(&v_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+          tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
+          tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
+        }
+      }
+      if (abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    if (lane == 0) {
+      const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // both operands K-major
+      const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // B operand MN-major
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), k_base = smem_u32(sK), v_base = smem_u32(sV);
+      uint32_t kv_iter = 0, n_items = 0;
+
+      auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
+          umma_ss(d_tmem, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc_kk,
+                  kk > 0);
+        }
+      };
+      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, umma_desc_sw128(b_base + (uint32_t)kk * 2048u, BLK_BYTES, 1024),
+                  idesc_mn, acc || kk > 0);
+        }
+      };
+
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        DqItem it;
+        dq_decode_item(a, (int)w, total_tiles, it);
+        if (it.nrows == 0) continue;
+        mbar_wait(&qdo_full, n_items & 1u, ab);
+        ++n_items;
+        tc_fence_after();
+        {
+          const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
+          mbar_wait(&k_full[st], ph, ab);
+          tc_fence_after();
+          issue_kk(TM_S + (kv_iter & 1u) * 128u, q_base, k_base + st * TILE_BYTES);
+          umma_commit(&s_full[kv_iter & 1u]);
+          mbar_wait(&v_full[st], ph, ab);
+          tc_fence_after();
+          issue_kk(TM_DP, do_base, v_base + st * TILE_BYTES);
+          umma_commit(&dp_full);
+          umma_commit(&v_empty[st]);
+        }
+        for (int j = it.jb; j < it.je; ++j, ++kv_iter) {
+          const uint32_t st = kv_iter & 1u;
+          const uint32_t nx = kv_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
+          const bool has_next = (j + 1 < it.je);
+          if (has_next) {
+            mbar_wait(&k_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_S + st_n * 128u, q_base, k_base + st_n * TILE_BYTES);
+            umma_commit(&s_full[st_n]);
+          }
+          mbar_wait(&ds_ready, kv_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DQ, TM_DP, k_base + st * TILE_BYTES, j > it.jb);
+          umma_commit(&k_empty[st]);
+          if (has_next) {
+            mbar_wait(&v_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_DP, do_base, v_base + st_n * TILE_BYTES);
+            umma_commit(&dp_full);
+            umma_commit(&v_empty[st_n]);
+          }
+        }
+        umma_commit(&acc_done);
+        umma_commit(&qdo_free);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------
+// 3. dK / dV
+// ---------------------------------------------------------------------------------------
+struct DkvItem {
+  int kvh, bos_q, bos_k, nsel, len_k, kv_start, i0, i_end;
+};
+
+// first index in [0, n) with pos[idx] >= x (pos ascending)
+__device__ __forceinline__ int lower_bound_pos(const int32_t* __restrict__ pos, int n, int x) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(pos + mid) < x) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void dkv_decode_item(const BwdArgs& a, int w, DkvItem& it) {
+  const int tile_g = w / a.h;
+  it.kvh = w % a.h;
+  const int seq = find_sequence(a.tile_off_k, a.n_seq, tile_g);
+  const int tile_l = tile_g - __ldg(a.tile_off_k + seq);
+  it.bos_q = __ldg(a.cu_q + seq);
+  it.nsel = max(__ldg(a.cu_q + seq + 1) - it.bos_q, 0);
+  it.bos_k = __ldg(a.cu_k + seq);
+  it.len_k = __ldg(a.cu_k + seq + 1) - it.bos_k;
+  it.kv_start = tile_l * TILE;
+  int first, last;  // compacted rows [first, last) can see some key of this tile
+  if (a.q_idx) {
+    const int32_t* pos = a.pos_ids + it.bos_q;
+    first = lower_bound_pos(pos, it.nsel, it.kv_start);
+    last = a.window > 0 ? lower_bound_pos(pos, it.nsel, it.kv_start + TILE + a.window) : it.nsel;
+  } else {
+    first = min(it.kv_start, it.nsel);
+    last = a.window > 0 ? min(it.nsel, it.kv_start + TILE + a.window) : it.nsel;
+  }
+  it.i0 = first / TILE;
+  it.i_end = (last + TILE - 1) / TILE;
+  if (last <= first) it.i_end = it.i0;
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                        const BwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;    // 2 stages
+  uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages
+
+  __shared__ uint64_t kv_full, kv_free, q_full[2], q_empty[2], do_full[2], do_empty[2];
+  __shared__ uint64_t st_full, dpt_full, p_ready, ds_ready, acc_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) float s_lse[2][TILE];
+  __shared__ __align__(16) float s_delta[2][TILE];
+  __shared__ __align__(16) int s_pos[2][TILE];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  AbortState ab{&abort_flag, a.status};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&kv_full, 1);
+    mbar_init(&kv_free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
+    }
+    mbar_init(&st_full, 1);
+    mbar_init(&dpt_full, 1);
+    mbar_init(&p_ready, 256);
+    mbar_init(&ds_ready, 256);
+    mbar_init(&acc_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t TM_ST = tmem, TM_DPT = tmem + 128u, TM_DK = tmem + 256u, TM_DV = tmem + 384u;
+
+  const int total_tiles = __ldg(a.n_ktiles);
+  const long long total_items = (long long)total_tiles * a.h;
+  const int G = a.hq / a.h;
+
+  if (warp < 8) {
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;   // key inside the tile
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int col0 = half * 64;
+    const float c = a.scale_log2;
+    uint32_t idx = 0, n_items = 0;
+
+    // loads lse / delta / pos of query tile `i` of head `hq` into registers (threads < 128)
+    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
+      const int r = i * TILE + tid;
+      if (r < it.nsel) {
+        const size_t sidx = (size_t)hq * a.cap + it.bos_q + r;
+        l = __ldg(a.lse_sel + sidx);
+        d = __ldg(a.delta_sel + sidx);
+        p = bwd_row_position(a, it.bos_q, r);
+      } else {
+        l = 0.f;
+        d = 0.f;
+        p = -1;
+      }
+    };
+
+    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      DkvItem it;
+      dkv_decode_item(a, (int)w, it);
+      const int nq = it.i_end - it.i0;
+      const int key_pos = it.kv_start + row;
+      const bool key_valid = key_pos < it.len_k;
+      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      if (nq <= 0) {
+        // no query can see this key tile: the gradients are zero
+        if (key_valid) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            reinterpret_cast<uint4*>(dk_row)[g] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(dv_row)[g] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      const int n_steps = nq * G;
+      const bool partial_keys = it.kv_start + TILE > it.len_k;
+
+      // vectors of the first step
+      if (tid < TILE) {
+        float l, d;
+        int p;
+        fetch_vec(it, it.kvh * G, it.i0, l, d, p);
+        s_lse[idx & 1u][tid] = l;
+        s_delta[idx & 1u][tid] = d;
+        s_pos[idx & 1u][tid] = p;
+      }
+      named_barrier_sync(3, 256);
+
+      for (int s = 0; s < n_steps; ++s, ++idx) {
+        const int g = s / nq, i = it.i0 + s % nq;
+        const uint32_t vb = idx & 1u;
+        // prefetch the vectors of the next step
+        float nl = 0.f, nd = 0.f;
+        int np = -1;
+        const bool has_next = (s + 1 < n_steps);
+        if (has_next && tid < TILE) fetch_vec(it, it.kvh * G + (s + 1) / nq, it.i0 + (s + 1) % nq, nl, nd, np);
+
+        const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
+        const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
+                            (a.window > 0 && pos_last > it.kv_start + a.window);
+        float p[64];
+        mbar_wait(&st_full, idx & 1u, ab);
+        tc_fence_after();
+#pragma unroll
+        for (int chk = 0; chk < 2; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(TM_ST + lane_off + (uint32_t)col0 + chk * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int ii = 0; ii < 32; ++ii) {
+            const int qc = col0 + chk * 32 + ii;
+            float pv = fast_exp2(fmaf(__uint_as_float(r[ii]), c, -s_lse[vb][qc]));
+            if (masked) {
+              const int qp = s_pos[vb][qc];
+              const bool ok = key_valid && key_pos <= qp && (a.window == 0 || key_pos >= qp - a.window);
+              if (!ok) pv = 0.f;
+            }
+            p[chk * 32 + ii] = pv;
+          }
+        }
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int ii = 0; ii < 32; ++ii) pk[ii] = pack_bf16x2(p[2 * ii], p[2 * ii + 1]);
+          named_barrier_sync(1, 256);   // all reads of S^T done before P^T overwrites it
+          tmem_st32(TM_ST + lane_off + (uint32_t)(half * 32), pk);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&p_ready);
+        }
+        mbar_wait(&dpt_full, idx & 1u, ab);
+        tc_fence_after();
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int chk = 0; chk < 2; ++chk) {
+            uint32_t r[32];
+            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0 + chk * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int ii = 0; ii < 16; ++ii) {
+              const int qc = col0 + chk * 32 + 2 * ii;
+              const float d0 = p[chk * 32 + 2 * ii] * (__uint_as_float(r[2 * ii]) - s_delta[vb][qc]);
+              const float d1 = p[chk * 32 + 2 * ii + 1] * (__uint_as_float(r[2 * ii + 1]) - s_delta[vb][qc + 1]);
+              pk[chk * 16 + ii] = pack_bf16x2(d0, d1);
+            }
+          }
+          if (has_next && tid < TILE) {
+            s_lse[vb ^ 1u][tid] = nl;
+            s_delta[vb ^ 1u][tid] = nd;
+            s_pos[vb ^ 1u][tid] = np;
+          }
+          named_barrier_sync(2, 256);   // all reads of dP^T done; next step's vectors visible
+          tmem_st32(TM_DPT + lane_off + (uint32_t)(half * 32), pk);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&ds_ready);
+        }
+      }
+
+      // ---- epilogue ----
+      mbar_wait(&acc_done, n_items & 1u, ab);
+      tc_fence_after();
+      ++n_items;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
+        const float mul = (which == 0) ? a.scale : 1.f;
+        __nv_bfloat16* dst_row = (which == 0) ? dk_row : dv_row;
+#pragma unroll
+        for (int chk = 0; chk < 2; ++chk) {
+          uint32_t r[32];
+          tmem_ld32(base + chk * 32, r);
+          tmem_ld_wait();
+          if (key_valid) {
+            uint4* dst = reinterpret_cast<uint4*>(dst_row + chk * 32);
+#pragma unroll
+            for (int gg = 0; gg < 4; ++gg) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * gg + 0]) * mul, __uint_as_float(r[8 * gg + 1]) * mul);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * gg + 2]) * mul, __uint_as_float(r[8 * gg + 3]) * mul);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * gg + 4]) * mul, __uint_as_float(r[8 * gg + 5]) * mul);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * gg + 6]) * mul, __uint_as_float(r[8 * gg + 7]) * mul);
+              dst[gg] = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      uint32_t q_iter = 0, n_items = 0;
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        DkvItem it;
+        dkv_decode_item(a, (int)w, it);
+        const int nq = it.i_end - it.i0;
+        if (nq <= 0) continue;
+        const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
+        mbar_wait(&kv_free, (n_items & 1u) ^ 1u, ab);
+        mbar_arrive_expect_tx(&kv_full, 2 * TILE_BYTES);
+        tma_load_2d(sK, &tm_k, &kv_full, xk, yk);
+        tma_load_2d(sK + BLK_BYTES, &tm_k, &kv_full, xk + 64, yk);
+        tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
+        tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
+        ++n_items;
+        for (int s = 0; s < nq * G; ++s, ++q_iter) {
+          const int g = s / nq, i = it.i0 + s % nq;
+          const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+          const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
+          mbar_wait(&q_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
+          tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
+          tma_load_2d(sQ + st * TILE_BYTES + BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
+          mbar_wait(&do_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
+          tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
+          tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
+        }
+      }
+      if (abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    if (lane == 0) {
+      const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);
+      const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+      uint32_t q_iter = 0, n_items = 0;
+
+      auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
+          umma_ss(d_tmem, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc_kk,
+                  kk > 0);
+        }
+      };
+      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, umma_desc_sw128(b_base + (uint32_t)kk * 2048u, BLK_BYTES, 1024),
+                  idesc_mn, acc || kk > 0);
+        }
+      };
+
+      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+        DkvItem it;
+        dkv_decode_item(a, (int)w, it);
+        const int nq = it.i_end - it.i0;
+        if (nq <= 0) continue;
+        const int n_steps = nq * G;
+        mbar_wait(&kv_full, n_items & 1u, ab);
+        ++n_items;
+        tc_fence_after();
+        {
+          const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+          mbar_wait(&q_full[st], ph, ab);
+          tc_fence_after();
+          issue_kk(TM_ST, k_base, q_base + st * TILE_BYTES);
+          umma_commit(&st_full);
+          mbar_wait(&do_full[st], ph, ab);
+          tc_fence_after();
+          issue_kk(TM_DPT, v_base, do_base + st * TILE_BYTES);
+          umma_commit(&dpt_full);
+        }
+        for (int s = 0; s < n_steps; ++s, ++q_iter) {
+          const uint32_t st = q_iter & 1u;
+          const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
+          const bool has_next = (s + 1 < n_steps);
+          mbar_wait(&p_ready, q_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DV, TM_ST, do_base + st * TILE_BYTES, s > 0);
+          umma_commit(&do_empty[st]);
+          if (has_next) {
+            mbar_wait(&q_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_ST, k_base, q_base + st_n * TILE_BYTES);
+            umma_commit(&st_full);
+          }
+          mbar_wait(&ds_ready, q_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DK, TM_DPT, q_base + st * TILE_BYTES, s > 0);
+          umma_commit(&q_empty[st]);
+          if (has_next) {
+            mbar_wait(&do_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_DPT, v_base, do_base + st_n * TILE_BYTES);
+            umma_commit(&dpt_full);
+          }
+        }
+        umma_commit(&acc_done);
+        umma_commit(&kv_free);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+struct BwdWorkspace {
+  __nv_bfloat16* q_sel;
+  __nv_bfloat16* do_sel;
+  float* lse_sel;
+  float* delta_sel;
+  int cap;
+  size_t bytes;
+};
+
+static BwdWorkspace bwd_workspace_layout(void* base, int n_tokens, int hq, bool gathered) {
+  BwdWorkspace w{};
+  w.cap = gathered ? n_tokens + TILE : n_tokens;
+  w.cap = (w.cap + 3) & ~3;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* r = p ? p + off : nullptr;
+    off += (bytes + 255) & ~size_t(255);
+    return r;
+  };
+  if (gathered) {
+    w.q_sel = reinterpret_cast<__nv_bfloat16*>(take((size_t)w.cap * hq * HEAD_DIM * 2));
+    w.do_sel = reinterpret_cast<__nv_bfloat16*>(take((size_t)w.cap * hq * HEAD_DIM * 2));
+  }
+  w.lse_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
+  w.delta_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
+  w.bytes = off;
+  return w;
+}
+
+static int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           const void* d_o, void* dq, void* dk, void* dv, const int64_t* q_idx,
+                           const int32_t* pos_ids, const int32_t* cu_q, const int32_t* cu_k, const int32_t* tile_off_q,
+                           const int32_t* n_qtiles, const int32_t* tile_off_k, const int32_t* n_ktiles,
+                           const int32_t* sq_ptr, int n_seq, int n_tokens, int hq, int h, int window, float scale,
+                           void* workspace, size_t workspace_bytes, int32_t* status, cudaStream_t stream) {
+  const bool gathered = (q_idx != nullptr);
+  BwdWorkspace ws = bwd_workspace_layout(workspace, n_tokens, hq, gathered);
+  LOGO_REQUIRE(workspace && workspace_bytes >= ws.bytes, LOGO_ERR_WORKSPACE,
+               "attention backward workspace too small: need %zu bytes", ws.bytes);
+  LOGO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, LOGO_ERR_INVALID,
+               "attention backward workspace must be 256-byte aligned");
+
+  if (gathered)
+    LOGO_CHECK_CUDA(cudaMemsetAsync(dq, 0, (size_t)n_tokens * hq * HEAD_DIM * sizeof(__nv_bfloat16), stream));
+
+  const int sms = sm_count();
+  bwd_preprocess_kernel<<<sms * 4, 256, 0, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, q_idx, sq_ptr, ws.q_sel,
+      ws.do_sel, ws.lse_sel, ws.delta_sel, ws.cap, n_tokens, hq, status);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+
+  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  const uint64_t q_row_bytes = (uint64_t)hq * HEAD_DIM * 2, kv_row_bytes = (uint64_t)h * HEAD_DIM * 2;
+  const void* q_src = gathered ? (const void*)ws.q_sel : q;
+  const void* do_src = gathered ? (const void*)ws.do_sel : d_o;
+  const uint64_t q_rows = gathered ? (uint64_t)ws.cap : (uint64_t)n_tokens;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&tm_q, q_src, (uint64_t)hq * HEAD_DIM, q_rows, q_row_bytes, 64, TILE))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tm_do, do_src, (uint64_t)hq * HEAD_DIM, q_rows, q_row_bytes, 64, TILE))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tm_k, k, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tm_v, v, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
+
+  static thread_local int attr_set_dev = -1;
+  int dev = 0;
+  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (attr_set_dev != dev) {
+    LOGO_CHECK_CUDA(
+        cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+    LOGO_CHECK_CUDA(
+        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+    attr_set_dev = dev;
+  }
+
+  BwdArgs a{};
+  a.q_idx = q_idx;
+  a.pos_ids = pos_ids;
+  a.cu_q = cu_q;
+  a.cu_k = cu_k;
+  a.tile_off_q = tile_off_q;
+  a.n_qtiles = n_qtiles;
+  a.tile_off_k = tile_off_k;
+  a.n_ktiles = n_ktiles;
+  a.lse_sel = ws.lse_sel;
+  a.delta_sel = ws.delta_sel;
+  a.cap = ws.cap;
+  a.dq = (__nv_bfloat16*)dq;
+  a.dk = (__nv_bfloat16*)dk;
+  a.dv = (__nv_bfloat16*)dv;
+  a.n_seq = n_seq;
+  a.n_tokens = n_tokens;
+  a.hq = hq;
+  a.h = h;
+  a.window = window;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+
+  attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  attn_bwd_dq_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  return LOGO_OK;
+}
+
+}  // namespace logo
+
+extern "C" size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered) {
+  if (n_tokens < 0 || hq <= 0) return 0;
+  return logo::bwd_workspace_layout(nullptr, n_tokens, hq, gathered != 0).bytes;
+}
+
+extern "C" int logo_sq_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                const void* d_o, void* dq, void* dk, void* dv, const int64_t* q_idx,
+                                const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                const int32_t* tile_off, const int32_t* meta, void* workspace, size_t workspace_bytes,
+                                int n_seq, int n_tokens, int hq, int h, int d, float scale, int32_t* status,
+                                logo_stream_t stream) {
+  using namespace logo;
+  LOGO_REQUIRE(d == HEAD_DIM, LOGO_ERR_UNSUPPORTED, "head_dim %d is not supported (only 128)", d);
+  LOGO_REQUIRE(hq > 0 && h > 0 && hq % h == 0, LOGO_ERR_INVALID, "hq (%d) must be a positive multiple of h (%d)", hq, h);
+  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+  if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
+  LOGO_REQUIRE(q && k && v && o && lse && d_o && dq && dk && dv, LOGO_ERR_INVALID, "tensor pointers must not be NULL");
+  LOGO_REQUIRE(q_idx && pos_ids && cu_seqlens_q && cu_seqlens_k && tile_off && meta, LOGO_ERR_INVALID,
+               "selection metadata pointers must not be NULL");
+  LOGO_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(d_o) && aligned16(dq) &&
+                   aligned16(dk) && aligned16(dv),
+               LOGO_ERR_INVALID, "tensors must be 16-byte aligned");
+  return launch_attn_bwd(q, k, v, o, lse, d_o, dq, dk, dv, q_idx, pos_ids, cu_seqlens_q, cu_seqlens_k,
+                         tile_off + 3 * (n_seq + 1), meta + 4, tile_off + (n_seq + 1), meta + 2, meta, n_seq, n_tokens,
+                         hq, h, 0, scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
+}
+
+extern "C" int logo_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                            const void* d_o, void* dq, void* dk, void* dv, const int32_t* cu_seqlens,
+                            const int32_t* tile_off, const int32_t* meta, void* workspace, size_t workspace_bytes,
+                            int n_seq, int n_tokens, int hq, int h, int d, int window, float scale, int32_t* status,
+                            logo_stream_t stream) {
+  using namespace logo;
+  LOGO_REQUIRE(d == HEAD_DIM, LOGO_ERR_UNSUPPORTED, "head_dim %d is not supported (only 128)", d);
+  LOGO_REQUIRE(hq > 0 && h > 0 && hq % h == 0, LOGO_ERR_INVALID, "hq (%d) must be a positive multiple of h (%d)", hq, h);
+  LOGO_REQUIRE(window > 0, LOGO_ERR_INVALID, "window must be positive, got %d", window);
+  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+  if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
+  LOGO_REQUIRE(q && k && v && o && lse && d_o && dq && dk && dv, LOGO_ERR_INVALID, "tensor pointers must not be NULL");
+  LOGO_REQUIRE(cu_seqlens && tile_off && meta, LOGO_ERR_INVALID, "cu_seqlens, tile_off and meta must not be NULL");
+  LOGO_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(d_o) && aligned16(dq) &&
+                   aligned16(dk) && aligned16(dv),
+               LOGO_ERR_INVALID, "tensors must be 16-byte aligned");
+  // identity selection: query tiles == key tiles (row 1 of tile_off, meta[2])
+  return launch_attn_bwd(q, k, v, o, lse, d_o, dq, dk, dv, nullptr, nullptr, cu_seqlens, cu_seqlens,
+                         tile_off + (n_seq + 1), meta + 2, tile_off + (n_seq + 1), meta + 2, nullptr, n_seq, n_tokens,
+                         hq, h, window, scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
+}

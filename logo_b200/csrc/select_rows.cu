@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(SEL_THREADS)
   }
 }
 
-// One block. Writes cu_seqlens_q, the two tile-offset arrays, meta and the gate sum.
+// One block. Writes cu_seqlens_q, the four tile-offset rows, meta and the gate sum.
 __global__ void __launch_bounds__(1024)
     finalize_kernel(const int32_t* __restrict__ cu, int n_seq, int n_tokens, const int64_t* __restrict__ q_idx,
                     int32_t* __restrict__ cu_q, int32_t* __restrict__ tile_off,
@@ -201,10 +201,12 @@ __global__ void __launch_bounds__(1024)
   __shared__ int s_scan_q[1024];
   __shared__ int s_scan_k[1024];
   __shared__ int s_scan_l[1024];
-  __shared__ int s_carry_q, s_carry_k, s_carry_l;
+  __shared__ int s_scan_t[1024];
+  __shared__ int s_carry_q, s_carry_k, s_carry_l, s_carry_t;
   int32_t* tile_off_q = tile_off;                      // selected rows, 256-row pairs
   int32_t* tile_off_k = tile_off + (n_seq + 1);        // keys, 128-row tiles
   int32_t* tile_off_l = tile_off + 2 * (n_seq + 1);    // all rows, 256-row pairs (local branch)
+  int32_t* tile_off_t = tile_off + 3 * (n_seq + 1);    // selected rows, 128-row tiles (backward)
   const SelWorkspace ws = sel_ws(ws_raw, nblocks);
   const int tid = threadIdx.x;
   const int sq = nblocks > 0 ? (int)(unsigned)(ws.state[nblocks - 1] & 0xffffffffull) : 0;
@@ -227,6 +229,8 @@ __global__ void __launch_bounds__(1024)
     s_carry_q = 0;
     s_carry_k = 0;
     s_carry_l = 0;
+    s_carry_t = 0;
+    tile_off_t[0] = 0;
     tile_off_q[0] = 0;
     tile_off_k[0] = 0;
     tile_off_l[0] = 0;
@@ -236,41 +240,47 @@ __global__ void __launch_bounds__(1024)
   // prefix sums of tiles per sequence, 1024 sequences per round
   for (int base = 0; base < n_seq; base += 1024) {
     const int s = base + tid;
-    int tq = 0, tk = 0, tl = 0;
+    int tq = 0, tk = 0, tl = 0, tt = 0;
     if (s < n_seq) {
       const int nq = max(cu_q[s + 1] - cu_q[s], 0);
       const int nk = max(cu[s + 1] - cu[s], 0);
       tq = (nq + 2 * LOGO_TILE - 1) / (2 * LOGO_TILE);
       tk = (nk + LOGO_TILE - 1) / LOGO_TILE;
       tl = (nk + 2 * LOGO_TILE - 1) / (2 * LOGO_TILE);
+      tt = (nq + LOGO_TILE - 1) / LOGO_TILE;
     }
     s_scan_q[tid] = tq;
     s_scan_k[tid] = tk;
     s_scan_l[tid] = tl;
+    s_scan_t[tid] = tt;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {
-      int aq = 0, ak = 0, al = 0;
+      int aq = 0, ak = 0, al = 0, at = 0;
       if (tid >= off) {
         aq = s_scan_q[tid - off];
         ak = s_scan_k[tid - off];
         al = s_scan_l[tid - off];
+        at = s_scan_t[tid - off];
       }
       __syncthreads();
       s_scan_q[tid] += aq;
       s_scan_k[tid] += ak;
       s_scan_l[tid] += al;
+      s_scan_t[tid] += at;
       __syncthreads();
     }
     if (s < n_seq) {
       tile_off_q[s + 1] = s_carry_q + s_scan_q[tid];
       tile_off_k[s + 1] = s_carry_k + s_scan_k[tid];
       tile_off_l[s + 1] = s_carry_l + s_scan_l[tid];
+      tile_off_t[s + 1] = s_carry_t + s_scan_t[tid];
     }
     __syncthreads();
     if (tid == 0) {
       s_carry_q += s_scan_q[1023];
       s_carry_k += s_scan_k[1023];
       s_carry_l += s_scan_l[1023];
+      s_carry_t += s_scan_t[1023];
     }
     __syncthreads();
   }
@@ -280,7 +290,8 @@ __global__ void __launch_bounds__(1024)
     meta[1] = s_carry_q;
     meta[2] = s_carry_k;
     meta[3] = s_carry_l;
-    meta[4] = meta[5] = meta[6] = meta[7] = 0;
+    meta[4] = s_carry_t;
+    meta[5] = meta[6] = meta[7] = 0;
     if (gate_sum) {
       float acc = 0.f;
       for (int b = 0; b < nblocks; ++b) acc += ws.partial[b];
