@@ -148,6 +148,64 @@ int logo_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
                  int d, int window, float scale, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Per-branch RMSNorm + gate mask + blend.
+ * Replaces logo/modules/layernorm.py:17-22 as used at logo/layers/logo.py:180-182 and :225-227,
+ * and the masked blend of logo/layers/logo.py:256-258:
+ *     g = gate >= thres ? gate : 0;   out = (1 - g) * norm_l(local) + g * norm_g(glob)
+ *   local, glob [n_tokens, h, 128] bf16 (glob rows of unselected tokens are never read)
+ *   gate [n_tokens] bf16; thres: device scalar (bf16 / fp16 / fp32)
+ *   w_local, w_global [128] of w_dtype (bf16 / fp32); ignored when use_norm == 0
+ *   out [n_tokens, h * 128] bf16
+ * The backward writes d_local, d_glob [n_tokens, h, 128] bf16 (d_glob = 0 on unselected tokens),
+ * d_gate [n_tokens] bf16 (0 where the gate was masked) and the two [128] weight gradients
+ * (w_dtype; may be NULL). workspace: logo_fuse_bwd_workspace_bytes(n_tokens) bytes.
+ * ------------------------------------------------------------------------------------------ */
+int logo_fuse_fwd(const void* local, const void* glob, const void* gate, int gate_dtype, const void* thres,
+                  int thres_dtype, const void* w_local, const void* w_global, int w_dtype, void* out, int n_tokens,
+                  int h, int d, float eps, int use_norm, logo_stream_t stream);
+
+size_t logo_fuse_bwd_workspace_bytes(int n_tokens);
+
+int logo_fuse_bwd(const void* d_out, const void* local, const void* glob, const void* gate, int gate_dtype,
+                  const void* thres, int thres_dtype, const void* w_local, const void* w_global, int w_dtype,
+                  void* d_local, void* d_glob, void* d_gate, void* d_w_local, void* d_w_global, int n_tokens, int h,
+                  int d, float eps, int use_norm, void* workspace, size_t workspace_bytes, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KV cache (bf16, head-major):
+ *   global branch: k_cache, v_cache [batch, h, t_max, 128]; token p of a sequence sits at row p
+ *   local branch : k_ring,  v_ring  [batch, h, ring, 128];  token p sits at row p % ring
+ *                  (ring = window + 1 keeps exactly the keys a decode step may see)
+ *
+ * logo_cache_append replaces the torch.cat updates of logo/cache.py:79-118 and the per-step
+ * transpose().contiguous() copies of logo/layers/logo.py:153-158: it writes t_new new tokens per
+ * sequence in place. Inputs are [batch, t_new, h, 128] views with element strides
+ * (stride_b, stride_t, stride_h), multiples of 8. Token t of sequence b lands at position
+ * (start_lens ? start_lens[b] : start) + t. Either pair (ring / cache) may be NULL.
+ *
+ * logo_decode_attn replaces the q_len == 1 path of logo/layers/logo.py:166-179 (local, 129 keys)
+ * and :228-249 (global): one query per sequence against the cache. Sequences whose
+ * gate[b] < *thres skip the global branch entirely and get o_global = 0 (the reference runs
+ * dense attention for every sequence whenever any gate passes and masks afterwards, :229-256).
+ *   q_local, q_global, o_local, o_global [batch, hq, 128] bf16
+ *   ctx_lens [batch] int32: cached tokens of each sequence INCLUDING the token just appended
+ *   max_ctx: upper bound of ctx_lens known to the host (sizes the grid); hq / h in {1, 2, 4}
+ *   workspace: logo_decode_workspace_bytes(batch, hq, max_ctx) bytes
+ * ------------------------------------------------------------------------------------------ */
+int logo_cache_append(const void* k_local, const void* v_local, const void* k_global, const void* v_global,
+                      long long stride_b, long long stride_t, long long stride_h, void* k_ring, void* v_ring,
+                      int ring, void* k_cache, void* v_cache, int t_max, const int32_t* start_lens, int start,
+                      int batch, int t_new, int h, int d, int32_t* status, logo_stream_t stream);
+
+size_t logo_decode_workspace_bytes(int batch, int hq, int max_ctx);
+
+int logo_decode_attn(const void* q_local, const void* q_global, const void* k_ring, const void* v_ring, int ring,
+                     const void* k_cache, const void* v_cache, int t_max, const int32_t* ctx_lens, const void* gate,
+                     int gate_dtype, const void* thres, int thres_dtype, void* o_local, void* o_global, int batch,
+                     int hq, int h, int d, int max_ctx, float scale, void* workspace, size_t workspace_bytes,
+                     int32_t* status, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Diagnostics: single-tile tcgen05 matrix multiply used by the GPU test-suite to pin the
  * shared-memory / tensor-memory operand encodings the attention kernels rely on.
  * No counterpart in the reference.

@@ -6,7 +6,7 @@ raised. Build the library with ``python -m logo_b200.build``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_size_t, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 from typing import Optional
 
@@ -36,6 +36,19 @@ _SIGNATURES = {
                                                    c_void_p]),
     "logo_swa_bwd": (c_int, [c_void_p] * 13 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                                c_void_p]),
+    "logo_fuse_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                              c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "logo_fuse_bwd_workspace_bytes": (c_size_t, [c_int]),
+    "logo_fuse_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                              c_void_p, c_size_t, c_void_p]),
+    "logo_cache_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_void_p, c_void_p]),
+    "logo_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "logo_decode_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
     "logo_umma_selftest": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
                                    c_void_p, c_void_p]),
 }

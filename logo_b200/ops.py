@@ -319,3 +319,64 @@ def sdpa_causal_ref(q, k, v, scale=None, cu_seqlens=None):
     outs = [F.scaled_dot_product_attention(qh[:, :, a:b], kh[:, :, a:b], vh[:, :, a:b], is_causal=True, scale=scale)
             for a, b in zip(cu[:-1], cu[1:])]
     return torch.cat(outs, dim=2).transpose(1, 2).contiguous()
+
+
+# ----------------------------------------------------------------------------------------
+# per-branch RMSNorm + gate mask + blend (logo/layers/logo.py:180-182,225-227,256-258)
+# ----------------------------------------------------------------------------------------
+class FuseFunction(torch.autograd.Function):
+    """out[N, H*D] = (1-g) * RMSNorm_l(local) + g * RMSNorm_g(glob), g = gate masked below thres."""
+
+    @staticmethod
+    def forward(ctx, local, glob, gate, thres, w_local, w_global, eps, use_norm):
+        lib = _lib.load()
+        _require_cuda(local, glob, gate, thres)
+        if local.dtype != torch.bfloat16 or glob.dtype != torch.bfloat16 or gate.dtype != torch.bfloat16:
+            raise TypeError("the fused norm/blend kernel takes bf16 activations and a bf16 gate")
+        local, glob = local.contiguous(), glob.contiguous()
+        gate_flat = gate.reshape(-1).contiguous()
+        thres = thres.reshape(-1)[:1].contiguous()
+        n, h, d = local.shape
+        if use_norm:
+            if w_local.dtype != w_global.dtype:
+                raise TypeError("both context-norm weights must share one dtype")
+            w_local, w_global = w_local.contiguous(), w_global.contiguous()
+            w_code = _lib.torch_dtype_code(w_local.dtype)
+        else:
+            w_code = _lib.DTYPE_BF16
+        out = torch.empty(n, h * d, dtype=torch.bfloat16, device=local.device)
+        rc = lib.logo_fuse_fwd(local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(), _lib.DTYPE_BF16,
+                               thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
+                               _lib.ptr(w_local) if use_norm else None, _lib.ptr(w_global) if use_norm else None,
+                               w_code, out.data_ptr(), n, h, d, float(eps), int(bool(use_norm)),
+                               _lib.current_stream_ptr(local.device))
+        _lib.check(rc, "logo_fuse_fwd")
+        ctx.save_for_backward(local, glob, gate_flat, thres, w_local if use_norm else None,
+                              w_global if use_norm else None)
+        ctx.eps, ctx.use_norm, ctx.gate_shape, ctx.w_code = float(eps), bool(use_norm), gate.shape, w_code
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        lib = _lib.load()
+        local, glob, gate_flat, thres, w_local, w_global = ctx.saved_tensors
+        n, h, d = local.shape
+        d_out = d_out.contiguous()
+        d_local, d_glob = torch.empty_like(local), torch.empty_like(glob)
+        d_gate = torch.empty_like(gate_flat)
+        d_wl = torch.empty_like(w_local) if ctx.use_norm else None
+        d_wg = torch.empty_like(w_global) if ctx.use_norm else None
+        ws_bytes = lib.logo_fuse_bwd_workspace_bytes(n)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=local.device)
+        rc = lib.logo_fuse_bwd(d_out.data_ptr(), local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(),
+                               _lib.DTYPE_BF16, thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
+                               _lib.ptr(w_local), _lib.ptr(w_global), ctx.w_code, d_local.data_ptr(),
+                               d_glob.data_ptr(), d_gate.data_ptr(), _lib.ptr(d_wl), _lib.ptr(d_wg), n, h, d, ctx.eps,
+                               int(ctx.use_norm), ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(local.device))
+        _lib.check(rc, "logo_fuse_bwd")
+        return d_local, d_glob, d_gate.view(ctx.gate_shape), None, d_wl, d_wg, None, None
+
+
+def fuse_norm_blend(local, glob, gate, thres, w_local, w_global, eps: float, use_norm: bool = True):
+    """local, glob [N,H,128] bf16; gate [N] or [N,1] bf16; thres one-element tensor. Returns [N, H*128]."""
+    return FuseFunction.apply(local, glob, gate, thres, w_local, w_global, eps, use_norm)

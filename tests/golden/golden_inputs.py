@@ -1,0 +1,106 @@
+"""Seeded inputs shared by ``make_golden.py`` (which feeds them to the reference) and by the
+tests (which feed them to the oracle and to the CUDA kernels). Only ``numpy.random.RandomState``
+is used, so the streams do not depend on the torch version."""
+from __future__ import annotations
+
+import numpy as np
+
+
+def _cu(lens):
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + int(n))
+    return cu
+
+
+# ----------------------------------------------------------------------------------------------
+# selection masks
+# ----------------------------------------------------------------------------------------------
+def selection_cases():
+    """name -> (bool mask [N], cu_seqlens list)."""
+    cases = {}
+    rs = np.random.RandomState(1)
+    cases["single_half"] = (rs.uniform(size=512) < 0.5, _cu([512]))
+    cases["varlen_empty_seq"] = (rs.uniform(size=200) < 0.4, [0, 70, 70, 200])
+    cases["all_selected"] = (np.ones(300, dtype=bool), _cu([100, 200]))
+    cases["none_selected"] = (np.zeros(260, dtype=bool), _cu([130, 130]))
+    lens = [1, 513, 0, 127, 128, 129, 2048, 3]
+    cases["ragged"] = (rs.uniform(size=sum(lens)) < 0.25, _cu(lens))
+    m = np.zeros(1000, dtype=bool)
+    m[[0, 499, 500, 999]] = True
+    cases["seq_ends_only"] = (m, _cu([500, 500]))
+    cases["many_blocks"] = (rs.uniform(size=9000) < 0.125, _cu([4096, 4904]))
+    return cases
+
+
+# ----------------------------------------------------------------------------------------------
+# sq_full_attn cases (reference Triton kernels under the interpreter)
+# ----------------------------------------------------------------------------------------------
+ATTN_CASES = {
+    #  name: (lens, HQ, H, D, selection ratio, seed)
+    "d32_gqa_empty_seq": ([70, 0, 130], 4, 2, 32, 0.5, 11),
+    "d128_two_seq": ([170, 130], 2, 1, 128, 0.5, 12),
+    "d128_all_rows": ([260], 2, 2, 128, 1.0, 13),
+    "d128_sparse": ([384], 1, 1, 128, 0.125, 14),
+}
+
+
+def attn_case_inputs(name):
+    lens, hq, h, d, ratio, seed = ATTN_CASES[name]
+    rs = np.random.RandomState(seed)
+    n = sum(lens)
+    q = rs.standard_normal((n, hq, d)).astype(np.float32)
+    k = rs.standard_normal((n, h, d)).astype(np.float32)
+    v = rs.standard_normal((n, h, d)).astype(np.float32)
+    do = rs.standard_normal((n, hq, d)).astype(np.float32)
+    sel = (rs.uniform(size=n) < ratio) if ratio < 1.0 else np.ones(n, dtype=bool)
+    return q, k, v, do, sel, _cu(lens)
+
+
+# ----------------------------------------------------------------------------------------------
+# layer cases
+# ----------------------------------------------------------------------------------------------
+LAYER_CASES = {
+    # the configuration quoted as the CPU-runnable case: B=1, T=512, hidden 2048, 16 x 128, window 128
+    "config1": dict(hidden=2048, heads=16, kv_heads=16, window=128, gate_thres=0.5, backend="triton",
+                    batch=1, seqlen=512, lens=None, seed=100, subsample=61),
+    "small_varlen": dict(hidden=256, heads=2, kv_heads=2, window=128, gate_thres=0.5, backend="triton",
+                         batch=1, seqlen=420, lens=[100, 0, 320], seed=101),
+    "small_batch": dict(hidden=256, heads=2, kv_heads=1, window=128, gate_thres=0.5, backend="flash",
+                        batch=2, seqlen=200, lens=None, seed=102),
+}
+
+
+def layer_weights(case):
+    """Reference parameter name -> fp32 array. Linear weights N(0, 0.02); the per-head global
+    projections are the reference's identity initialisation perturbed by N(0, 0.02)."""
+    rs = np.random.RandomState(case["seed"])
+    hid, nh, nkv = case["hidden"], case["heads"], case["kv_heads"]
+    d = hid // nh
+    w = {}
+    w["q_proj.weight"] = (0.02 * rs.standard_normal((nh * d, hid))).astype(np.float32)
+    w["k_proj.weight"] = (0.02 * rs.standard_normal((nkv * d, hid))).astype(np.float32)
+    w["v_proj.weight"] = (0.02 * rs.standard_normal((nkv * d, hid))).astype(np.float32)
+    w["o_proj.weight"] = (0.02 * rs.standard_normal((hid, hid))).astype(np.float32)
+    w["gate_proj.weight"] = (0.02 * rs.standard_normal((1, hid))).astype(np.float32)
+    eye = np.eye(d, dtype=np.float32)
+    w["q_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nh, d, d))).astype(np.float32)
+    w["k_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
+    w["v_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
+    w["context_norm_local.weight"] = (1 + 0.1 * rs.standard_normal(d)).astype(np.float32)
+    w["context_norm_global.weight"] = (1 + 0.1 * rs.standard_normal(d)).astype(np.float32)
+    return w
+
+
+def layer_case_inputs(case):
+    """(hidden [B,T,hidden] fp32, cu_seqlens list or None, position_ids [B,T] int64)."""
+    rs = np.random.RandomState(case["seed"] + 1000)
+    b, t = case["batch"], case["seqlen"]
+    hidden = rs.standard_normal((b, t, case["hidden"])).astype(np.float32)
+    if case["lens"] is not None:
+        cu = _cu(case["lens"])
+        pos = np.concatenate([np.arange(n) for n in case["lens"]]).astype(np.int64)[None]
+    else:
+        cu = None
+        pos = np.broadcast_to(np.arange(t, dtype=np.int64)[None], (b, t)).copy()
+    return hidden, cu, pos

@@ -1,0 +1,158 @@
+"""The drop-in LoGoAttention layer against outputs of the reference layer (fixtures) and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from golden_inputs import LAYER_CASES, layer_case_inputs, layer_weights
+from oracle import logo_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def build_layer(case, device, dtype=torch.bfloat16, backend=None):
+    from logo_b200 import LoGoAttention
+    from logo_b200.config import LoGoConfig
+
+    cfg = LoGoConfig(hidden_size=case["hidden"], num_attention_heads=case["heads"],
+                     num_key_value_heads=case["kv_heads"], window_size=case["window"], global_qk_param="linear_proj",
+                     gate_thres_init=case["gate_thres"], sparse_full_attn_backend=backend or case["backend"],
+                     num_hidden_layers=1, rms_norm_eps=1e-5, max_position_embeddings=8192)
+    layer = LoGoAttention(cfg, layer_idx=0)
+    params = dict(layer.named_parameters())
+    with torch.no_grad():
+        for name, arr in layer_weights(case).items():
+            params[name].copy_(torch.from_numpy(arr))
+    return layer.to(device=device, dtype=dtype).eval()
+
+
+def test_parameter_and_buffer_names_match_reference(cuda_device):
+    layer = build_layer(LAYER_CASES["small_varlen"], cuda_device)
+    names = {n: tuple(p.shape) for n, p in layer.named_parameters()}
+    assert names == {
+        "q_proj.weight": (256, 256), "k_proj.weight": (256, 256), "v_proj.weight": (256, 256),
+        "o_proj.weight": (256, 256), "q_global_proj": (2, 128, 128), "k_global_proj": (2, 128, 128),
+        "v_global_proj": (2, 128, 128), "gate_proj.weight": (1, 256), "context_norm_local.weight": (128,),
+        "context_norm_global.weight": (128,)}
+    bufs = {n for n, _ in layer.named_buffers()}
+    assert {"gate_thres", "gate_avg", "global_token_count", "total_token_count"} <= bufs
+    assert "gate_thres" in layer.state_dict() and "gate_avg" not in layer.state_dict()
+
+
+@pytest.mark.parametrize("name", sorted(LAYER_CASES))
+def test_layer_forward_vs_reference_layer(cuda_device, golden, name):
+    """bf16 CUDA layer vs the fp32 reference layer on the same seeded weights and inputs.
+
+    The selected-row set must equal the reference's except for tokens whose gate lies within bf16
+    rounding of the threshold (the gate GEMV runs in bf16 here, fp32 there)."""
+    case = LAYER_CASES[name]
+    g = golden["layer"]
+    layer = build_layer(case, cuda_device)
+    hidden, cu, pos = layer_case_inputs(case)
+    kwargs = dict(position_ids=torch.from_numpy(pos).to(cuda_device))
+    if cu is not None:
+        kwargs["cu_seqlens"] = torch.tensor(cu, dtype=torch.int32, device=cuda_device)
+    h = torch.from_numpy(hidden).to(cuda_device, torch.bfloat16)
+    with torch.no_grad():
+        out, attn_w, past = layer(h, **kwargs)
+        gate = torch.sigmoid(layer.gate_proj(h)).float().reshape(-1).cpu().numpy()
+    assert attn_w is None and past is None and out.shape == h.shape and out.dtype == torch.bfloat16
+    ref_gate = g[f"{name}/gate"]
+    ref_sel = np.zeros(ref_gate.size, dtype=bool)
+    ref_sel[g[f"{name}/q_idx"]] = True
+    mine = gate >= case["gate_thres"]
+    differ = np.nonzero(mine != ref_sel)[0]
+    assert np.all(np.abs(ref_gate[differ] - case["gate_thres"]) < 4e-3), "selection differs away from the threshold"
+    out = out.float().cpu().numpy()
+    keep = np.ones(ref_gate.size, dtype=bool)
+    keep[differ] = False            # a flipped token legitimately takes the other branch
+    if case.get("subsample"):
+        flat_keep = np.repeat(keep, case["hidden"])[:: case["subsample"]]
+        err = np.abs(out.reshape(-1)[:: case["subsample"]] - g[f"{name}/out_sub"])[flat_keep]
+    else:
+        err = np.abs(out - g[f"{name}/out"]).reshape(-1, case["hidden"])[keep]
+    # bf16 end to end (projections, RoPE, attention, norm, o_proj) against fp32: 1e-2 on O(0.3) outputs
+    assert err.max() <= 1.5e-2, err.max()
+    assert np.sqrt(np.mean(err ** 2)) < 4e-3
+
+
+def test_layer_backward_vs_oracle(cuda_device):
+    """Training step of the layer: gradients w.r.t. the input and every parameter vs fp32 autograd
+    through the oracle (same selection: it is computed from the bf16 gate in both)."""
+    case = LAYER_CASES["small_varlen"]
+    layer = build_layer(case, cuda_device).train()
+    hidden, cu, pos = layer_case_inputs(case)
+    h = torch.from_numpy(hidden).to(cuda_device, torch.bfloat16).requires_grad_(True)
+    out, _, _ = layer(h, position_ids=torch.from_numpy(pos).to(cuda_device),
+                      cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=cuda_device))
+    rs = np.random.RandomState(0)
+    d_out = torch.from_numpy(rs.standard_normal(out.shape).astype(np.float32)).to(torch.bfloat16)
+    out.backward(d_out.to(cuda_device))
+    n = hidden.shape[1]
+    assert layer.total_token_count.item() == n
+    assert 0 < layer.global_token_count.item() < n
+    gate = torch.sigmoid(layer.gate_proj(h.detach())).float()
+    assert abs(layer.gate_avg.item() - gate.sum().item()) < 0.5
+    assert layer.global_token_count.item() == int((gate.reshape(-1) >= case["gate_thres"]).sum().item())
+
+    # oracle in fp32 on the bf16-rounded weights and input
+    w = {k: v.detach().float().cpu().requires_grad_(True) for k, v in layer.named_parameters()}
+    hr = h.detach().float().cpu()[0].requires_grad_(True)
+    ref = orc.logo_layer_ref(hr, w, cu, case["heads"], case["kv_heads"], case["window"], case["gate_thres"], 1e-5)
+    ref.backward(d_out.float()[0])
+    assert orc.err_ratio(ref.detach(), out[0].float().cpu()) < 2e-2
+    assert orc.err_ratio(hr.grad, h.grad[0].float().cpu()) < 3e-2
+    for name, p in layer.named_parameters():
+        r = orc.err_ratio(w[name].grad, p.grad.float().cpu())
+        assert r < 4e-2, (name, r)
+
+
+def test_prefill_then_decode_vs_reference(cuda_device, golden):
+    """Prefill 150 tokens into the cache, then 6 single-token steps (mixed active / inactive
+    sequences) against the reference layer + reference Cache fixtures."""
+    from logo_b200 import Cache
+
+    g = golden["decode"]
+    case = LAYER_CASES["small_batch"]
+    layer = build_layer(case, cuda_device)
+    B, T0, steps = 2, 150, 6
+    hidden = torch.from_numpy(np.random.RandomState(4242).standard_normal((B, T0 + steps, case["hidden"]))
+                              .astype(np.float32)).to(cuda_device, torch.bfloat16)
+    cache = Cache()
+    with torch.no_grad():
+        pos = torch.arange(T0, device=cuda_device)[None].expand(B, -1)
+        y, _, past = layer(hidden[:, :T0], position_ids=pos, past_key_value=cache, use_cache=True)
+        assert past is cache and cache.get_seq_length(0) == T0
+        assert np.abs(y.float().cpu().numpy() - g["decode/prefill_out"]).max() <= 1.5e-2
+        outs = []
+        for s in range(steps):
+            pos = torch.full((B, 1), T0 + s, device=cuda_device)
+            y, _, _ = layer(hidden[:, T0 + s: T0 + s + 1], position_ids=pos, past_key_value=cache, use_cache=True)
+            outs.append(y.float().cpu().numpy())
+    got = np.concatenate(outs, axis=1)
+    ref_gate = g["decode/gate"][:, T0:, 0]
+    near = np.abs(ref_gate - case["gate_thres"]) < 4e-3          # tokens whose branch may legitimately flip
+    err = np.abs(got - g["decode/step_out"])[~near]
+    assert err.max() <= 1.5e-2, err.max()
+    assert cache.get_seq_length(0) == T0 + steps
+    st = cache[0]
+    assert tuple(st["attn_state"][0].shape) == tuple(g["decode/local_k_shape"])
+    assert tuple(st["attn_state_full"][0].shape) == tuple(g["decode/full_k_shape"])
+
+
+def test_backend_string_and_dtype_errors(cuda_device):
+    from logo_b200.config import LoGoConfig
+
+    case = LAYER_CASES["small_batch"]
+    a = build_layer(case, cuda_device, backend="flash")
+    b = build_layer(case, cuda_device, backend="triton")
+    hidden, _, pos = layer_case_inputs(case)
+    h = torch.from_numpy(hidden).to(cuda_device, torch.bfloat16)
+    p = torch.from_numpy(pos).to(cuda_device)
+    with torch.no_grad():
+        assert torch.equal(a(h, position_ids=p)[0], b(h, position_ids=p)[0])
+    with pytest.raises(ValueError):
+        LoGoConfig(sparse_full_attn_backend="eager")
+    with pytest.raises(TypeError, match="bf16"):
+        build_layer(case, cuda_device, dtype=torch.float32)(h.float(), position_ids=p)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        build_layer(case, "cpu")(h.cpu(), position_ids=p.cpu())
