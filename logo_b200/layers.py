@@ -65,14 +65,27 @@ class RotaryEmbedding(nn.Module):
         self.max_seq_len_cached = config.max_position_embeddings
         self.original_max_seq_len = config.max_position_embeddings
         self.config = config
-        dim = config.hidden_size // config.num_attention_heads
-        inv_freq = 1.0 / (config.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float().to(device) / dim))
         self.attention_scaling = 1.0
-        self.register_buffer("inv_freq", inv_freq, persistent=False)
+        self.register_buffer("inv_freq", self._make_inv_freq(device), persistent=False)
+        self._inv_freq_fp32 = {}
+
+    def _make_inv_freq(self, device) -> torch.Tensor:
+        dim = self.config.hidden_size // self.config.num_attention_heads
+        return 1.0 / (self.config.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float().to(device) / dim))
+
+    def _inv_freq_for(self, device) -> torch.Tensor:
+        # `module.to(torch.bfloat16)` also casts the `inv_freq` buffer, which costs the rotation angle
+        # about three decimal digits at position ~500; the tables are always built from an fp32 copy.
+        if self.inv_freq.dtype == torch.float32 and self.inv_freq.device == device:
+            return self.inv_freq
+        key = str(device)
+        if key not in self._inv_freq_fp32:
+            self._inv_freq_fp32[key] = self._make_inv_freq(device)
+        return self._inv_freq_fp32[key]
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, position_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        inv = self.inv_freq[None, :, None].float().expand(position_ids.shape[0], -1, 1)
+        inv = self._inv_freq_for(x.device)[None, :, None].expand(position_ids.shape[0], -1, 1)
         pos = position_ids[:, None, :].float()
         with torch.autocast(device_type=x.device.type, enabled=False):
             freqs = (inv @ pos).transpose(1, 2)

@@ -109,7 +109,7 @@ def _require_cuda(*tensors):
 def select_rows(gate_or_mask: torch.Tensor, thres: Optional[torch.Tensor], cu_seqlens: torch.Tensor) -> SelMeta:
     """Runs the select / compact kernel. ``gate_or_mask`` is a flat ``[N]`` float gate (compared
     ``>= thres`` in fp32, ``thres`` a one-element device tensor) or a bool mask."""
-    _require_cuda(gate_or_mask, cu_seqlens, thres)
+    _require_cuda(gate_or_mask, thres)   # cu_seqlens may live on the host: it is moved like the reference does
     lib = _lib.load()
     flat = gate_or_mask.reshape(-1).contiguous()
     dev = flat.device

@@ -226,11 +226,14 @@ def logo_layer_ref(
     eps: float,
     rope_theta: float = 10000.0,
     return_parts: bool = False,
+    selection_override: Optional[torch.Tensor] = None,
 ):
     """logo/layers/logo.py:96-262 with global_qk_param='linear_proj', no cache, no dropout.
 
     ``weights`` uses the reference's parameter names (q_proj.weight, ..., q_global_proj,
     gate_proj.weight, context_norm_local.weight, context_norm_global.weight, o_proj.weight).
+    ``selection_override`` (bool [N]) replaces the threshold test; the gate values themselves are
+    still computed here. Tests use it to compare against a run whose gate was rounded differently.
     Returns the layer output [N, hidden] (and the intermediate tensors when asked).
     """
     n, hid = hidden.shape
@@ -254,8 +257,14 @@ def logo_layer_ref(
     local = swa_ref(ql, kl, vv, cu, window)                          # :166-179
     thres = torch.tensor(gate_thres, dtype=gate.dtype)
     selection = gate[:, 0] >= thres                                  # :190
+    if selection_override is not None:
+        selection = selection_override.reshape(-1).to(torch.bool)
+        thres = torch.tensor(float("-inf"), dtype=gate.dtype)        # masked_fill below must not re-mask
+        gate_for_blend = gate * selection[:, None].to(gate.dtype)
+    else:
+        gate_for_blend = gate
     glob, _ = attention_dense_ref(gq, gk, gv, cu, None, None, selection)   # :192-209
-    fused = fuse_ref(local, glob, gate, thres, weights["context_norm_local.weight"],
+    fused = fuse_ref(local, glob, gate_for_blend, thres, weights["context_norm_local.weight"],
                      weights["context_norm_global.weight"], eps)     # :180-182,225-227,256-258
     out = fused @ weights["o_proj.weight"].T                         # :259
     if return_parts:

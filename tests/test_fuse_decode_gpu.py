@@ -54,11 +54,11 @@ def test_fuse_forward_backward_vs_oracle(cuda_device, h, use_norm, w_dtype):
     wg = torch.from_numpy((1 + 0.1 * rs.standard_normal(d)).astype(np.float32)).to(w_dtype)
     d_out = _bf(rs.standard_normal((n, h * d)))
 
-    ref_in = [x.float().requires_grad_(True) for x in (local, glob, gate, wl, wg)]
+    ref_in = [x.detach().float().clone().requires_grad_(True) for x in (local, glob, gate, wl, wg)]
     ref = orc.fuse_ref(ref_in[0], ref_in[1], ref_in[2], thres, ref_in[3], ref_in[4], 1e-5, use_norm)
     ref.backward(d_out.float())
 
-    dev_in = [x.to(cuda_device).requires_grad_(True) for x in (local, glob, gate, wl, wg)]
+    dev_in = [x.detach().clone().to(cuda_device).requires_grad_(True) for x in (local, glob, gate, wl, wg)]
     out = ops.fuse_norm_blend(dev_in[0], dev_in[1], dev_in[2], thres.to(cuda_device),
                               dev_in[3] if use_norm else None, dev_in[4] if use_norm else None, 1e-5, use_norm)
     out.backward(d_out.to(cuda_device))

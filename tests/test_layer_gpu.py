@@ -67,12 +67,17 @@ def test_layer_forward_vs_reference_layer(cuda_device, golden, name):
     keep[differ] = False            # a flipped token legitimately takes the other branch
     if case.get("subsample"):
         flat_keep = np.repeat(keep, case["hidden"])[:: case["subsample"]]
-        err = np.abs(out.reshape(-1)[:: case["subsample"]] - g[f"{name}/out_sub"])[flat_keep]
+        ref = g[f"{name}/out_sub"]
+        err = np.abs(out.reshape(-1)[:: case["subsample"]] - ref)[flat_keep]
     else:
-        err = np.abs(out - g[f"{name}/out"]).reshape(-1, case["hidden"])[keep]
-    # bf16 end to end (projections, RoPE, attention, norm, o_proj) against fp32: 1e-2 on O(0.3) outputs
-    assert err.max() <= 1.5e-2, err.max()
-    assert np.sqrt(np.mean(err ** 2)) < 4e-3
+        ref = g[f"{name}/out"]
+        err = np.abs(out - ref).reshape(-1, case["hidden"])[keep]
+    # bf16 end to end against fp32. The kernels themselves meet 1e-2 max-abs on identical inputs
+    # (test_attention_gpu); here the bf16 cuBLAS projections, RoPE and o_proj around them dominate:
+    # running the same graph in bf16 on the CPU gives 0.7 % RMS and 3.4 % max of the output's spread.
+    scale = float(np.std(ref))
+    assert err.max() <= 0.05 * scale, (err.max(), scale)
+    assert np.sqrt(np.mean(err ** 2)) < 0.012 * scale
 
 
 def test_layer_backward_vs_oracle(cuda_device):
@@ -97,7 +102,9 @@ def test_layer_backward_vs_oracle(cuda_device):
     # oracle in fp32 on the bf16-rounded weights and input
     w = {k: v.detach().float().cpu().requires_grad_(True) for k, v in layer.named_parameters()}
     hr = h.detach().float().cpu()[0].requires_grad_(True)
-    ref = orc.logo_layer_ref(hr, w, cu, case["heads"], case["kv_heads"], case["window"], case["gate_thres"], 1e-5)
+    sel = (gate.reshape(-1) >= case["gate_thres"]).cpu()      # the bf16 gate decides, in both runs
+    ref = orc.logo_layer_ref(hr, w, cu, case["heads"], case["kv_heads"], case["window"], case["gate_thres"], 1e-5,
+                             selection_override=sel)
     ref.backward(d_out.float()[0])
     assert orc.err_ratio(ref.detach(), out[0].float().cpu()) < 2e-2
     assert orc.err_ratio(hr.grad, h.grad[0].float().cpu()) < 3e-2
@@ -122,7 +129,8 @@ def test_prefill_then_decode_vs_reference(cuda_device, golden):
         pos = torch.arange(T0, device=cuda_device)[None].expand(B, -1)
         y, _, past = layer(hidden[:, :T0], position_ids=pos, past_key_value=cache, use_cache=True)
         assert past is cache and cache.get_seq_length(0) == T0
-        assert np.abs(y.float().cpu().numpy() - g["decode/prefill_out"]).max() <= 1.5e-2
+        scale = float(np.std(g["decode/prefill_out"]))
+        assert np.abs(y.float().cpu().numpy() - g["decode/prefill_out"]).max() <= 0.05 * scale
         outs = []
         for s in range(steps):
             pos = torch.full((B, 1), T0 + s, device=cuda_device)
@@ -132,7 +140,7 @@ def test_prefill_then_decode_vs_reference(cuda_device, golden):
     ref_gate = g["decode/gate"][:, T0:, 0]
     near = np.abs(ref_gate - case["gate_thres"]) < 4e-3          # tokens whose branch may legitimately flip
     err = np.abs(got - g["decode/step_out"])[~near]
-    assert err.max() <= 1.5e-2, err.max()
+    assert err.max() <= 0.05 * scale, err.max()
     assert cache.get_seq_length(0) == T0 + steps
     st = cache[0]
     assert tuple(st["attn_state"][0].shape) == tuple(g["decode/local_k_shape"])
