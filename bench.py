@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the LoGo attention hot path: ``sq_full_attn`` forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--ratio R] [--impl reference]
+
+Workload (the configuration the metric is quoted on): bf16 Q/K/V, 4 sequences x 8192 tokens
+packed to ``[1, 32768, 16, 128]``, causal, Q/K ~ N(0,1) * 128**-0.25 (so that q.k has the
+variance of N(0,1)/sqrt(128)-scaled inputs), V, dO ~ N(0,1), a Bernoulli(R) row mask.
+One step = select/compact + forward + backward over one such batch. Synthetic, seeded.
+
+Metric: TFLOP/s on the EFFECTIVE FLOPs of the selected rows,
+``F_fwd = 4 * 128 * HQ * sum_{selected rows}(pos + 1)``, ``F_step = 3.5 * F_fwd``.
+Masked / padded tile work and the recomputation of S in the backward are not counted.
+
+With N > 1 (one process per GPU under torchrun) every rank runs its own batch (weak
+scaling, no collective on the data path); the value is the sum of FLOPs over ranks divided
+by the slowest rank's device time.
+
+``--impl reference`` times the CPU restatement of the reference's algorithm (the oracle) on
+the host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np
+import torch
+
+T_SEQ, N_SEQ, HQ, H, D = 8192, 4, 16, 16, 128
+N_TOK = T_SEQ * N_SEQ
+SCALE = D ** -0.5
+METRIC = "sq_full_attn_fwd_bwd_effective_tflops"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(bf16=d.get("bf16_tflops", 1590.0), bf16_sustained=d.get("bf16_tflops_sustained", 1400.0),
+                    hbm=d.get("hbm_gbs", 6650.0), source="measured")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU leg: the oracle on a bounded sample (used for cpu_baseline and for --impl reference)
+# ----------------------------------------------------------------------------------------------
+def cpu_sample_step(ratio: float, seed: int, t: int = 2048, heads: int = 4):
+    """One forward + backward of the oracle on one sequence of `t` tokens and `heads` heads.
+    Returns (seconds, effective FLOPs)."""
+    from oracle import logo_oracle as orc
+
+    rs = np.random.RandomState(seed)
+    mk = lambda s: torch.from_numpy((rs.standard_normal((t, heads, D)) * s).astype(np.float32))
+    q, k, v, do = mk(D ** -0.25).requires_grad_(True), mk(D ** -0.25).requires_grad_(True), \
+        mk(1.0).requires_grad_(True), mk(1.0)
+    sel = torch.from_numpy(rs.uniform(size=t) < ratio) if ratio < 1.0 else torch.ones(t, dtype=torch.bool)
+    t0 = time.perf_counter()
+    o, _ = orc.attention_dense_ref(q, k, v, [0, t], SCALE, None, sel)
+    o.backward(do)
+    dt = time.perf_counter() - t0
+    pos = torch.nonzero(sel).flatten().double()
+    flops = 3.5 * 4.0 * D * heads * float((pos + 1).sum())
+    return dt, flops
+
+
+def run_cpu(steps: int, warmup: int, ratio: float):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for i in range(warmup):
+        cpu_sample_step(ratio, 1000 + i)
+    total_t, total_f = 0.0, 0.0
+    for i in range(steps):
+        dt, fl = cpu_sample_step(ratio, i)
+        total_t += dt
+        total_f += fl
+    return total_f / total_t / 1e12, total_t / max(steps, 1) * 1e3, cores
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks sampling during the timed region
+# ----------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                get = getattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    self.nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = get(self.handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.001)
+
+    def finish(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def make_batch(device, ratio, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    mk = lambda h, s: (torch.randn(N_TOK, h, D, device=device, generator=g) * s).to(torch.bfloat16)
+    q, k, v, do = mk(HQ, D ** -0.25), mk(H, D ** -0.25), mk(H, 1.0), mk(HQ, 1.0)
+    sel = (torch.rand(N_TOK, device=device, generator=g) < ratio) if ratio < 1.0 else \
+        torch.ones(N_TOK, dtype=torch.bool, device=device)
+    cu = torch.arange(0, N_TOK + 1, T_SEQ, dtype=torch.int32, device=device)
+    return q, k, v, do, sel, cu
+
+
+def effective_flops_fwd(sel):
+    pos = (torch.nonzero(sel).flatten() % T_SEQ).double()
+    return 4.0 * D * HQ * float((pos + 1).sum().item())
+
+
+def device_step(batch):
+    """The hot path with inputs resident in HBM: select -> forward -> backward (raw C-ABI launches)."""
+    from logo_b200 import ops, ops_bwd
+
+    q, k, v, do, sel, cu = batch
+    m = ops.select_rows(sel, None, cu)
+    o, lse = ops.sq_attn_fwd_raw(q, k, v, m, SCALE)
+    dq, dk, dv = ops_bwd.sq_attn_bwd_raw(q, k, v, o, lse, do, m, SCALE)
+    return m, o, dq, dk, dv
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+    from logo_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    peaks = measured_peaks()
+
+    batch = make_batch(device, args.ratio, seed=1234 + rank)
+    f_fwd = effective_flops_fwd(batch[4])
+    f_step = 3.5 * f_fwd
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: inputs resident in HBM ----
+    for _ in range(args.warmup):
+        m, *_ = device_step(batch)
+    torch.cuda.synchronize()
+    ops.check_device_status(m.status, "warm-up")
+    lib.logo_profile_read(None, None, 0)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    lib.logo_profile_enable(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        m, *_ = device_step(batch)
+    e1.record()
+    barrier()
+    lib.logo_profile_enable(0)
+    clocks = sampler.finish()
+    ms_total = e0.elapsed_time(e1)
+    ops.check_device_status(m.status, "timed region")
+    import ctypes
+    tot = (ctypes.c_double * 5)()
+    cnt = (ctypes.c_int * 5)()
+    lib.logo_profile_read(ctypes.cast(tot, ctypes.c_void_p), ctypes.cast(cnt, ctypes.c_void_p), 5)
+    kernel_ms = {name: (tot[i] / cnt[i] if cnt[i] else None)
+                 for i, name in enumerate(["select", "attn_fwd", "bwd_preprocess", "bwd_dkv", "bwd_dq"])}
+    launches = 2 * cnt[0] + cnt[1] + cnt[2] + cnt[3] + cnt[4]     # select = 2 kernels per call
+
+    # ---- e2e: public API, host buffers, copies inside the timed region ----
+    host = [t.cpu().pin_memory() for t in batch[:5]]
+    cu_host = batch[5].cpu()
+    outs_host = None
+
+    def e2e_step():
+        nonlocal outs_host
+        q, k, v, do, sel = (t.to(device, non_blocking=True) for t in host)
+        q, k, v = q[None].requires_grad_(True), k[None].requires_grad_(True), v[None].requires_grad_(True)
+        o = ops.sq_full_attn(q, k, v, sel[None], scale=SCALE, cu_seqlens=cu_host)
+        o.backward(do[None])
+        res = (o.detach(), q.grad, k.grad, v.grad)
+        if outs_host is None:
+            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        for dst, src in zip(outs_host, res):
+            dst.copy_(src, non_blocking=True)
+
+    if args.skip_e2e:
+        ms_e2e, h2d, d2h = float("nan"), 0, 0
+    else:
+        for _ in range(max(args.warmup, 1)):
+            e2e_step()
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e3.record()
+        barrier()
+        ms_e2e = e2.elapsed_time(e3)
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        d2h = sum(t.numel() * t.element_size() for t in outs_host)
+
+    # ---- reduce over ranks: slowest rank's time, summed FLOPs ----
+    stats = torch.tensor([ms_total, ms_e2e, f_step], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, ms_e2e, f_sum = mx[0].item(), mx[1].item(), sm[2].item()
+    else:
+        f_sum = f_step
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value = f_sum * args.steps / (ms_total * 1e-3) / 1e12
+    e2e_value = f_sum * args.steps / (ms_e2e * 1e-3) / 1e12
+
+    # dominant kernel: backward dK/dV (4 of the 7 executed products). Its algorithmic work per launch
+    # is the four products it has to form over the visible (query, key) pairs: 2 * F_fwd.
+    dom = "bwd_dkv"
+    dom_flops = 2.0 * f_fwd
+    achieved = dom_flops / (kernel_ms[dom] * 1e-3) / 1e12 if kernel_ms[dom] else None
+    roofline = {"bound": "tensor", "kernel": "attn_bwd_dkv_kernel", "achieved": achieved, "peak": peaks["bf16"],
+                "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None, "traffic": None,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 burst"}
+    kernel_tflops = {
+        "attn_fwd": f_fwd / (kernel_ms["attn_fwd"] * 1e-3) / 1e12 if kernel_ms["attn_fwd"] else None,
+        "bwd_dkv": achieved,
+        "bwd_dq": 1.5 * f_fwd / (kernel_ms["bwd_dq"] * 1e-3) / 1e12 if kernel_ms["bwd_dq"] else None,
+    }
+
+    if args.skip_cpu:
+        cpu_value, cpu_ms, cores = None, float("nan"), 0
+    else:
+        cpu_value, cpu_ms, cores = run_cpu(steps=3, warmup=1, ratio=args.ratio)
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "sq_full_attn fwd+bwd, 4x8192 tokens packed [1,32768,16,128], causal, "
+                               f"Bernoulli({args.ratio}) row mask", "ratio": args.ratio,
+                   "l2": "inputs (671 MB per step) exceed the 126 MB L2; no flush needed",
+                   "effective_flops_per_step": f_step},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "kernel_ms": kernel_ms, "kernel_tflops": kernel_tflops,
+        "frac_of_peak_fwd_bwd": value / world / peaks["bf16"],
+        "cpu_baseline": {"value": cpu_value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "oracle fwd+bwd on 1 sequence x 2048 tokens x 4 heads, fp32, 3 steps "
+                                   f"({cpu_ms:.0f} ms each)"},
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    value, ms, cores = run_cpu(args.steps, args.warmup, args.ratio)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "sq_full_attn fwd+bwd, 4x8192 tokens packed [1,32768,16,128], causal, "
+                               f"Bernoulli({args.ratio}) row mask", "ratio": args.ratio},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "each step = oracle fwd+bwd on 1 sequence x 2048 tokens x 4 heads, fp32"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--ratio", type=float, default=0.5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: leave out the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -206,6 +206,17 @@ int logo_decode_attn(const void* q_local, const void* q_global, const void* k_ri
                      int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Per-kernel timing for benchmarks (no counterpart in the reference). While enabled on the
+ * calling host thread, every launch of the kernels below is bracketed by CUDA events on its
+ * stream. logo_profile_read waits for those events, returns per kernel kind the summed device
+ * time in ms and the number of launches since the last read, and releases the events.
+ *   kind 0 select + finalize, 1 attention forward, 2 backward preprocess,
+ *        3 backward dK/dV, 4 backward dQ
+ * ------------------------------------------------------------------------------------------ */
+int logo_profile_enable(int on);
+int logo_profile_read(double* total_ms, int* launches, int n);
+
+/* ------------------------------------------------------------------------------------------
  * Diagnostics: single-tile tcgen05 matrix multiply used by the GPU test-suite to pin the
  * shared-memory / tensor-memory operand encodings the attention kernels rely on.
  * No counterpart in the reference.

@@ -684,7 +684,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
         ++n_items;
         for (int s = 0; s < nq * G; ++s, ++q_iter) {
-          const int g = s / nq, i = it.i0 + s % nq;
+          const int g = s / nq, i = it.i0 + s % nq;   // query head of the group, query tile
           const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
           const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
           mbar_wait(&q_empty[st], ph ^ 1u, ab);
@@ -832,9 +832,11 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
     LOGO_CHECK_CUDA(cudaMemsetAsync(dq, 0, (size_t)n_tokens * hq * HEAD_DIM * sizeof(__nv_bfloat16), stream));
 
   const int sms = sm_count();
+  prof_begin(PROF_BWD_PRE, stream);
   bwd_preprocess_kernel<<<sms * 4, 256, 0, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, q_idx, sq_ptr, ws.q_sel,
       ws.do_sel, ws.lse_sel, ws.delta_sel, ws.cap, n_tokens, hq, status);
+  prof_end(PROF_BWD_PRE, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
 
   CUtensorMap tm_q, tm_do, tm_k, tm_v;
@@ -883,9 +885,13 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
 
+  prof_begin(PROF_BWD_DKV, stream);
   attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  prof_end(PROF_BWD_DKV, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
+  prof_begin(PROF_BWD_DQ, stream);
   attn_bwd_dq_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  prof_end(PROF_BWD_DQ, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
 }

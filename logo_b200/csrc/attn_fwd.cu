@@ -438,7 +438,9 @@ static int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     attr_set_dev = dev;
   }
   const int grid = sm_count();
+  prof_begin(PROF_ATTN_FWD, stream);
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tm_k, tm_v, a);
+  prof_end(PROF_ATTN_FWD, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
 }

@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 namespace logo {
 
@@ -63,7 +64,61 @@ int sm_count() {
   return cached[dev];
 }
 
+// ---------------------------------------------------------------------------------------
+// optional per-kernel timing with CUDA events (off by default, per host thread)
+// ---------------------------------------------------------------------------------------
+struct ProfSlot {
+  cudaEvent_t start, stop;
+};
+static thread_local bool g_prof_on = false;
+static thread_local std::vector<ProfSlot>* g_prof = nullptr;   // [PROF_KINDS] vectors
+
+bool prof_enabled() { return g_prof_on; }
+
+void prof_begin(int kind, cudaStream_t stream) {
+  if (!g_prof_on || kind < 0 || kind >= PROF_KINDS) return;
+  ProfSlot s{};
+  if (cudaEventCreate(&s.start) != cudaSuccess || cudaEventCreate(&s.stop) != cudaSuccess) return;
+  cudaEventRecord(s.start, stream);
+  g_prof[kind].push_back(s);
+}
+
+void prof_end(int kind, cudaStream_t stream) {
+  if (!g_prof_on || kind < 0 || kind >= PROF_KINDS || g_prof[kind].empty()) return;
+  cudaEventRecord(g_prof[kind].back().stop, stream);
+}
+
 }  // namespace logo
+
+extern "C" int logo_profile_enable(int on) {
+  using namespace logo;
+  if (!g_prof) g_prof = new std::vector<ProfSlot>[PROF_KINDS];
+  g_prof_on = (on != 0);
+  return LOGO_OK;
+}
+
+extern "C" int logo_profile_read(double* total_ms, int* launches, int n) {
+  using namespace logo;
+  for (int k = 0; k < n; ++k) {
+    double total = 0.0;
+    int count = 0;
+    if (g_prof && k < PROF_KINDS) {
+      for (ProfSlot& s : g_prof[k]) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(s.stop) == cudaSuccess && cudaEventElapsedTime(&ms, s.start, s.stop) == cudaSuccess) {
+          total += ms;
+          ++count;
+        }
+        cudaEventDestroy(s.start);
+        cudaEventDestroy(s.stop);
+      }
+      g_prof[k].clear();
+    }
+    if (total_ms) total_ms[k] = total;
+    if (launches) launches[k] = count;
+  }
+  return LOGO_OK;
+}
 
 extern "C" int logo_version(void) { return 100; }
 

@@ -36,6 +36,12 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Per-kernel event timing (see logo_profile_enable): kernels report under these indices.
+enum ProfKind { PROF_SELECT = 0, PROF_ATTN_FWD = 1, PROF_BWD_PRE = 2, PROF_BWD_DKV = 3, PROF_BWD_DQ = 4, PROF_KINDS = 5 };
+bool prof_enabled();
+void prof_begin(int kind, cudaStream_t stream);
+void prof_end(int kind, cudaStream_t stream);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace logo

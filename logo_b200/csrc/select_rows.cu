@@ -332,6 +332,7 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
 
   const int nblocks = sel_num_blocks(n_tokens);
   LOGO_CHECK_CUDA(cudaMemsetAsync(workspace, 0, logo_select_workspace_bytes(n_tokens), stream));
+  prof_begin(PROF_SELECT, stream);
   if (nblocks > 0) {
 #define LOGO_LAUNCH_SELECT(T, ISB)                                                                        \
   select_kernel<T, ISB><<<nblocks, SEL_THREADS, 0, stream>>>(static_cast<const T*>(gate), thres, thres_dtype, \
@@ -346,7 +347,9 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
 #undef LOGO_LAUNCH_SELECT
     LOGO_CHECK_CUDA(cudaGetLastError());
   }
-  finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum, workspace, nblocks, status);
+  finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum,
+                                          workspace, nblocks, status);
+  prof_end(PROF_SELECT, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
 }
