@@ -92,6 +92,33 @@ int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int th
                      size_t workspace_bytes, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * logo_select_rows without a caller workspace. It has no counterpart in the reference.
+ *
+ * For hosts that may not allocate device memory themselves -- a plugin inside a serving
+ * process whose memory budget is fixed at start-up, or a step on a latency-critical path where
+ * cudaMalloc / cudaFree are off limits because they serialise the device -- the scan scratch
+ * lives in a static device array inside the library (about 6 KB; every GPU that loads the
+ * library holds it until the process exits). Inputs and outputs are still the caller's and
+ * mean exactly what they mean for logo_select_rows; results are identical.
+ *
+ *   - n_tokens must not exceed LOGO_SELECT_STATIC_MAX_TOKENS; larger inputs are refused with
+ *     LOGO_ERR_UNSUPPORTED and an explanatory logo_last_error() text.
+ *   - The call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ *     before any stream capture begins.
+ *   - All calls on a device share the one array, and it still holds what the previous call
+ *     wrote: the function clears the part it needs on `stream` first. Two calls that can overlap
+ *     on the GPU (different streams, or different host threads) race on it -- serialise them.
+ * ------------------------------------------------------------------------------------------ */
+#define LOGO_SELECT_STATIC_MAX_TOKENS (1 << 20)
+
+int logo_select_rows_static(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
+                            const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
+                            int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta, float* gate_sum,
+                            int32_t* status, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Query-sparse causal attention, forward (global branch).
  * Replaces logo/ops/selected_full_attn.py:33-121 (sq_full_attn_fwd_kernel), :340-362 (_fwd) and the
  * gather / scatter of :461,469-470 (SQFullAttentionFunction.forward).

@@ -28,6 +28,8 @@ _SIGNATURES = {
     "logo_select_workspace_bytes": (c_size_t, [c_int]),
     "logo_select_rows": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "logo_select_rows_static": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "logo_sq_attn_fwd": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                                    c_void_p]),
     "logo_swa_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),

@@ -13,6 +13,8 @@
 
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 namespace logo {
 
 constexpr int SEL_THREADS = 256;
@@ -350,6 +352,100 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
   finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum,
                                           workspace, nblocks, status);
   prof_end(PROF_SELECT, stream);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  return LOGO_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Variant of logo_select_rows for callers that cannot hand over a workspace.
+//
+// Some hosts of this library are not allowed to allocate device memory at all: a plugin
+// inside a serving process whose memory budget is fixed at start-up, or a step function on a
+// latency-critical path where cudaMalloc / cudaFree are banned because they serialise the
+// whole device. For them the scan scratch (ticket, per-block look-back words, per-block gate
+// partials) lives in the file-scope array below instead of a caller buffer. Every GPU that
+// loads the library holds these LOGO_SELECT_STATIC_BYTES until the process exits.
+//
+// `g_select_scratch` is a device symbol: inside host code the name is only a stand-in, not
+// an address a kernel could use. The device address is looked up with cudaGetSymbolAddress,
+// once per device with that device current, and cached; kernels receive that pointer.
+// ---------------------------------------------------------------------------------------
+namespace logo {
+
+constexpr int SELECT_STATIC_MAX_TOKENS = LOGO_SELECT_STATIC_MAX_TOKENS;
+constexpr size_t SELECT_STATIC_BYTES =
+    SEL_WS_HEADER + (size_t)((SELECT_STATIC_MAX_TOKENS + SEL_CHUNK - 1) / SEL_CHUNK) * (sizeof(unsigned long long) + sizeof(float)) + 16;
+
+static __device__ __align__(256) unsigned char g_select_scratch[SELECT_STATIC_BYTES];
+
+static std::mutex g_select_scratch_mu;
+static void* g_select_scratch_ptr[64] = {nullptr};
+
+// Device address of g_select_scratch on the current device (set-up on the first call per device).
+static int select_static_scratch(void** out) {
+  int dev = 0;
+  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
+  LOGO_REQUIRE(dev >= 0 && dev < 64, LOGO_ERR_UNSUPPORTED, "device ordinal %d is outside the supported range", dev);
+  std::lock_guard<std::mutex> lk(g_select_scratch_mu);
+  if (g_select_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_select_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return set_error(LOGO_ERR_CUDA, "cudaGetSymbolAddress(g_select_scratch) failed on device %d: %s", dev,
+                       cudaGetErrorString(e));
+    g_select_scratch_ptr[dev] = p;
+  }
+  *out = g_select_scratch_ptr[dev];
+  return LOGO_OK;
+}
+
+}  // namespace logo
+
+extern "C" int logo_select_rows_static(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
+                                       const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx,
+                                       int32_t* pos_ids, int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta,
+                                       float* gate_sum, int32_t* status, logo_stream_t stream_) {
+  using namespace logo;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+  LOGO_REQUIRE(n_tokens <= SELECT_STATIC_MAX_TOKENS, LOGO_ERR_UNSUPPORTED,
+               "logo_select_rows_static handles at most %d tokens per call (got %d); use logo_select_rows with a "
+               "caller workspace for larger inputs",
+               SELECT_STATIC_MAX_TOKENS, n_tokens);
+  LOGO_REQUIRE(cu_seqlens && cu_seqlens_q && tile_off && meta, LOGO_ERR_INVALID,
+               "cu_seqlens, cu_seqlens_q, tile_off and meta must not be NULL");
+  LOGO_REQUIRE(n_tokens == 0 || (gate && q_idx && pos_ids), LOGO_ERR_INVALID,
+               "gate, q_idx and pos_ids must not be NULL");
+  LOGO_REQUIRE(gate_dtype >= LOGO_DTYPE_BF16 && gate_dtype <= LOGO_DTYPE_BOOL, LOGO_ERR_INVALID,
+               "unknown gate dtype %d", gate_dtype);
+  if (gate_dtype != LOGO_DTYPE_BOOL) {
+    LOGO_REQUIRE(thres != nullptr, LOGO_ERR_INVALID, "thres must not be NULL for a floating-point gate");
+    LOGO_REQUIRE(thres_dtype >= LOGO_DTYPE_BF16 && thres_dtype <= LOGO_DTYPE_F16, LOGO_ERR_INVALID,
+                 "unknown threshold dtype %d", thres_dtype);
+  }
+  void* scratch = nullptr;
+  int rc = select_static_scratch(&scratch);
+  if (rc) return rc;
+
+  const int nblocks = sel_num_blocks(n_tokens);
+  // The array keeps what the previous call left: the ticket and the look-back words must start at zero.
+  LOGO_CHECK_CUDA(cudaMemsetAsync(scratch, 0, logo_select_workspace_bytes(n_tokens), stream));
+  if (nblocks > 0) {
+#define LOGO_LAUNCH_SELECT_STATIC(T, ISB)                                                                  \
+  select_kernel<T, ISB><<<nblocks, SEL_THREADS, 0, stream>>>(static_cast<const T*>(gate), thres, thres_dtype, \
+                                                             cu_seqlens, n_seq, n_tokens, q_idx, pos_ids,  \
+                                                             scratch, nblocks, status)
+    switch (gate_dtype) {
+      case LOGO_DTYPE_BF16: LOGO_LAUNCH_SELECT_STATIC(__nv_bfloat16, false); break;
+      case LOGO_DTYPE_F16: LOGO_LAUNCH_SELECT_STATIC(__half, false); break;
+      case LOGO_DTYPE_F32: LOGO_LAUNCH_SELECT_STATIC(float, false); break;
+      default: LOGO_LAUNCH_SELECT_STATIC(uint8_t, true); break;
+    }
+#undef LOGO_LAUNCH_SELECT_STATIC
+    LOGO_CHECK_CUDA(cudaGetLastError());
+  }
+  finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum,
+                                          scratch, nblocks, status);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
 }
