@@ -77,6 +77,40 @@ __device__ __forceinline__ bool tile_active(const FwdItem& it, int t, int j) {
   return it.nrows[t] > 0 && j >= it.jb[t] && j < it.je[t];
 }
 
+// keys outside [key_lo, key_hi] get a score of -inf
+__device__ __forceinline__ void mask_chunk(uint32_t (&r)[32], int k0, int key_hi, int key_lo) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int key = k0 + i;
+    if (!(key <= key_hi && key >= key_lo)) r[i] = 0xff800000u;
+  }
+}
+
+__device__ __forceinline__ float max_chunk(const uint32_t (&r)[32]) {
+  float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
+#pragma unroll
+  for (int i = 4; i < 32; i += 4) {
+    m0 = fmaxf(m0, __uint_as_float(r[i]));
+    m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+    m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
+    m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// p = 2^(s*c - mc) for 32 scores, packed to 16 bf16x2 words; the fp32 values are summed into l0 / l1
+__device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], float c, float mc, uint32_t (&pk)[16],
+                                               float& l0, float& l1) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), c, -mc));
+    const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), c, -mc));
+    l0 += p0;
+    l1 += p1;
+    pk[i] = pack_bf16x2(p0, p1);
+  }
+}
+
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const AttnArgs a) {
@@ -190,25 +224,20 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         mbar_wait(&s_full[t], n_steps & 1u, ab);
         tc_fence_after();
 
-        // ---- pass 1: row maximum of the raw scores ----
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int chk = 0; chk < 4; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(tS + chk * 32, r);
-          tmem_ld_wait();
-          if (masked) {
-            const int k0 = j * TILE + chk * 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = k0 + i;
-              if (key <= key_hi && key >= key_lo) mx = fmaxf(mx, __uint_as_float(r[i]));
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-          }
+        // ---- the whole score row (128 fp32) comes into registers with one wait ----
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld32(tS, s0);
+        tmem_ld32(tS + 32, s1);
+        tmem_ld32(tS + 64, s2);
+        tmem_ld32(tS + 96, s3);
+        tmem_ld_wait();
+        if (masked) {
+          mask_chunk(s0, j * TILE, key_hi, key_lo);
+          mask_chunk(s1, j * TILE + 32, key_hi, key_lo);
+          mask_chunk(s2, j * TILE + 64, key_hi, key_lo);
+          mask_chunk(s3, j * TILE + 96, key_hi, key_lo);
         }
+        const float mx = fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
 
         // ---- running maximum, lazy rescale of O ----
         if (first) {
@@ -239,32 +268,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
         }
 
-        // ---- pass 2: probabilities -> bf16 in tensor memory (over S), row sum ----
+        // ---- probabilities -> bf16 in tensor memory (over S), row sum ----
         const float mc = (m_run == -INFINITY) ? 0.f : m_run * c;
         float l0 = 0.f, l1 = 0.f;
-#pragma unroll 1
-        for (int chk = 0; chk < 4; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(tS + chk * 32, r);
-          tmem_ld_wait();
+        {
           uint32_t pk[16];
-          const int k0 = j * TILE + chk * 32;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float s0 = __uint_as_float(r[2 * i]);
-            float s1 = __uint_as_float(r[2 * i + 1]);
-            if (masked) {
-              const int key0 = k0 + 2 * i, key1 = key0 + 1;
-              if (!(key0 <= key_hi && key0 >= key_lo)) s0 = -INFINITY;
-              if (!(key1 <= key_hi && key1 >= key_lo)) s1 = -INFINITY;
-            }
-            const float p0 = fast_exp2(fmaf(s0, c, -mc));
-            const float p1 = fast_exp2(fmaf(s1, c, -mc));
-            l0 += p0;
-            l1 += p1;
-            pk[i] = pack_bf16x2(p0, p1);
-          }
-          tmem_st16(tS + chk * 16, pk);
+          exp_pack_chunk(s0, c, mc, pk, l0, l1);
+          tmem_st16(tS, pk);
+          exp_pack_chunk(s1, c, mc, pk, l0, l1);
+          tmem_st16(tS + 16, pk);
+          exp_pack_chunk(s2, c, mc, pk, l0, l1);
+          tmem_st16(tS + 32, pk);
+          exp_pack_chunk(s3, c, mc, pk, l0, l1);
+          tmem_st16(tS + 48, pk);
         }
         l_run += l0 + l1;
         tmem_st_wait();

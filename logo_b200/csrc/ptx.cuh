@@ -63,16 +63,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                : "memory");
 }
 
+// One try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes
+// or roughly `LOGO_TRYWAIT_HINT_NS` have passed, instead of burning issue slots in a poll loop.
+#ifndef LOGO_TRYWAIT_HINT_NS
+#define LOGO_TRYWAIT_HINT_NS 1000000u  // 1 ms
+#endif
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(LOGO_TRYWAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
@@ -83,22 +89,22 @@ struct AbortState {
   int* gmem_status;          // status word in global memory (may be null)
 };
 
-// Bounded wait. Returns false if the CTA is (or becomes) aborted.
+// Bounded wait. Returns false if the CTA is (or becomes) aborted. The clock is only consulted
+// after a number of failed (each up to LOGO_TRYWAIT_HINT_NS long) attempts.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortState& ab) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*ab.smem_abort) return false;
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
-  for (;;) {
+  for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*ab.smem_abort) return false;
-    if (globaltimer_ns() - t0 > LOGO_WAIT_TIMEOUT_NS) {
-      *ab.smem_abort = 1;
-      if (ab.gmem_status) atomicCAS(ab.gmem_status, 0, (int)DEV_WAIT_TIMEOUT);
-      return false;
+    if ((it & 15u) == 15u) {
+      if (*ab.smem_abort) return false;
+      if (globaltimer_ns() - t0 > LOGO_WAIT_TIMEOUT_NS) {
+        *ab.smem_abort = 1;
+        if (ab.gmem_status) atomicCAS(ab.gmem_status, 0, (int)DEV_WAIT_TIMEOUT);
+        return false;
+      }
     }
   }
 }
