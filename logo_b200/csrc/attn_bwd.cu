@@ -54,6 +54,81 @@ __device__ __forceinline__ int bwd_row_position(const BwdArgs& a, int bos_q, int
   return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;
 }
 
+
+// r[i] <- bits of p = 2^(s*c - lse) for 32 scores of one row; keys outside [key_lo, key_hi] give 0
+__device__ __forceinline__ void prob_chunk_row(uint32_t (&r)[32], float c, float lse, bool masked, int k0, int key_hi,
+                                               int key_lo) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float pv = fast_exp2(fmaf(__uint_as_float(r[i]), c, -lse));
+    if (masked) {
+      const int key = k0 + i;
+      if (!(key <= key_hi && key >= key_lo)) pv = 0.f;
+    }
+    r[i] = __float_as_uint(pv);
+  }
+}
+
+// pk[i] <- bf16x2 of p * (dp - delta) for 32 elements of one row
+__device__ __forceinline__ void ds_pack_chunk_row(const uint32_t (&p)[32], const uint32_t (&dp)[32], float delta,
+                                                  uint32_t* pk) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float d0 = __uint_as_float(p[2 * i]) * (__uint_as_float(dp[2 * i]) - delta);
+    const float d1 = __uint_as_float(p[2 * i + 1]) * (__uint_as_float(dp[2 * i + 1]) - delta);
+    pk[i] = pack_bf16x2(d0, d1);
+  }
+}
+
+// Column-wise variants for the transposed tiles of the dK/dV kernel: lse / delta / position differ per
+// column and come from shared memory (16-byte broadcast loads).
+__device__ __forceinline__ void prob_chunk_col(uint32_t (&r)[32], float c, const float* __restrict__ lse_s,
+                                               const int* __restrict__ pos_s, bool masked, bool key_valid,
+                                               int key_pos, int window) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 4 * g);
+    const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+    int pv4[4] = {0, 0, 0, 0};
+    if (masked) {
+      const int4 q4 = *reinterpret_cast<const int4*>(pos_s + 4 * g);
+      pv4[0] = q4.x;
+      pv4[1] = q4.y;
+      pv4[2] = q4.z;
+      pv4[3] = q4.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float pv = fast_exp2(fmaf(__uint_as_float(r[4 * g + e]), c, -lv[e]));
+      if (masked) {
+        const int qp = pv4[e];
+        const bool ok = key_valid && key_pos <= qp && (window == 0 || key_pos >= qp - window);
+        if (!ok) pv = 0.f;
+      }
+      r[4 * g + e] = __float_as_uint(pv);
+    }
+  }
+}
+
+__device__ __forceinline__ void ds_pack_chunk_col(const uint32_t (&p)[32], const uint32_t (&dp)[32],
+                                                  const float* __restrict__ delta_s, uint32_t* pk) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const float4 d4 = *reinterpret_cast<const float4*>(delta_s + 4 * g);
+    const float d0 = __uint_as_float(p[4 * g]) * (__uint_as_float(dp[4 * g]) - d4.x);
+    const float d1 = __uint_as_float(p[4 * g + 1]) * (__uint_as_float(dp[4 * g + 1]) - d4.y);
+    const float d2 = __uint_as_float(p[4 * g + 2]) * (__uint_as_float(dp[4 * g + 2]) - d4.z);
+    const float d3 = __uint_as_float(p[4 * g + 3]) * (__uint_as_float(dp[4 * g + 3]) - d4.w);
+    pk[2 * g] = pack_bf16x2(d0, d1);
+    pk[2 * g + 1] = pack_bf16x2(d2, d3);
+  }
+}
+
+__device__ __forceinline__ void pack_chunk(const uint32_t (&p)[32], uint32_t* pk) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(p[2 * i]), __uint_as_float(p[2 * i + 1]));
+}
+
 // ---------------------------------------------------------------------------------------
 // 1. preprocess
 // ---------------------------------------------------------------------------------------
@@ -226,39 +301,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const bool masked =
             (j * TILE + TILE - 1 > it.min_pos) || (a.window > 0 && j * TILE < it.max_pos - a.window);
         const uint32_t tS = TM_S + (idx & 1u) * 128u + lane_off + (uint32_t)col0;
-        float p[64];
+        uint32_t p0[32], p1[32];
         mbar_wait(&s_full[idx & 1u], (idx >> 1) & 1u, ab);
         tc_fence_after();
-#pragma unroll
-        for (int chk = 0; chk < 2; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(tS + chk * 32, r);
-          tmem_ld_wait();
-          const int k0 = j * TILE + col0 + chk * 32;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float pv = fast_exp2(fmaf(__uint_as_float(r[i]), c, -lse_r));
-            if (masked) {
-              const int key = k0 + i;
-              if (!(key <= key_hi && key >= key_lo)) pv = 0.f;
-            }
-            p[chk * 32 + i] = pv;
-          }
-        }
+        tmem_ld32(tS, p0);
+        tmem_ld32(tS + 32, p1);
+        tmem_ld_wait();
+        prob_chunk_row(p0, c, lse_r, masked, j * TILE + col0, key_hi, key_lo);
+        prob_chunk_row(p1, c, lse_r, masked, j * TILE + col0 + 32, key_hi, key_lo);
         mbar_wait(&dp_full, idx & 1u, ab);
         tc_fence_after();
         uint32_t pk[32];
-#pragma unroll
-        for (int chk = 0; chk < 2; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(TM_DP + lane_off + (uint32_t)col0 + chk * 32, r);
+        {
+          uint32_t d0[32], d1[32];
+          tmem_ld32(TM_DP + lane_off + (uint32_t)col0, d0);
+          tmem_ld32(TM_DP + lane_off + (uint32_t)col0 + 32, d1);
           tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float d0 = p[chk * 32 + 2 * i] * (__uint_as_float(r[2 * i]) - delta_r);
-            const float d1 = p[chk * 32 + 2 * i + 1] * (__uint_as_float(r[2 * i + 1]) - delta_r);
-            pk[chk * 16 + i] = pack_bf16x2(d0, d1);
-          }
+          ds_pack_chunk_row(p0, d0, delta_r, pk);
+          ds_pack_chunk_row(p1, d1, delta_r, pk + 16);
         }
         // every warp has finished reading dP before anyone overwrites it with dS
         named_barrier_sync(1, 256);
@@ -573,30 +633,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
                             (a.window > 0 && pos_last > it.kv_start + a.window);
-        float p[64];
+        uint32_t p0[32], p1[32];
         mbar_wait(&st_full, idx & 1u, ab);
         tc_fence_after();
-#pragma unroll
-        for (int chk = 0; chk < 2; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(TM_ST + lane_off + (uint32_t)col0 + chk * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int ii = 0; ii < 32; ++ii) {
-            const int qc = col0 + chk * 32 + ii;
-            float pv = fast_exp2(fmaf(__uint_as_float(r[ii]), c, -s_lse[vb][qc]));
-            if (masked) {
-              const int qp = s_pos[vb][qc];
-              const bool ok = key_valid && key_pos <= qp && (a.window == 0 || key_pos >= qp - a.window);
-              if (!ok) pv = 0.f;
-            }
-            p[chk * 32 + ii] = pv;
-          }
-        }
+        tmem_ld32(TM_ST + lane_off + (uint32_t)col0, p0);
+        tmem_ld32(TM_ST + lane_off + (uint32_t)col0 + 32, p1);
+        tmem_ld_wait();
+        prob_chunk_col(p0, c, &s_lse[vb][col0], &s_pos[vb][col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p1, c, &s_lse[vb][col0 + 32], &s_pos[vb][col0 + 32], masked, key_valid, key_pos, a.window);
         {
           uint32_t pk[32];
-#pragma unroll
-          for (int ii = 0; ii < 32; ++ii) pk[ii] = pack_bf16x2(p[2 * ii], p[2 * ii + 1]);
+          pack_chunk(p0, pk);
+          pack_chunk(p1, pk + 16);
           named_barrier_sync(1, 256);   // all reads of S^T done before P^T overwrites it
           tmem_st32(TM_ST + lane_off + (uint32_t)(half * 32), pk);
           tmem_st_wait();
@@ -607,18 +655,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tc_fence_after();
         {
           uint32_t pk[32];
-#pragma unroll
-          for (int chk = 0; chk < 2; ++chk) {
-            uint32_t r[32];
-            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0 + chk * 32, r);
+          {
+            uint32_t d0[32], d1[32];
+            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0, d0);
+            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0 + 32, d1);
             tmem_ld_wait();
-#pragma unroll
-            for (int ii = 0; ii < 16; ++ii) {
-              const int qc = col0 + chk * 32 + 2 * ii;
-              const float d0 = p[chk * 32 + 2 * ii] * (__uint_as_float(r[2 * ii]) - s_delta[vb][qc]);
-              const float d1 = p[chk * 32 + 2 * ii + 1] * (__uint_as_float(r[2 * ii + 1]) - s_delta[vb][qc + 1]);
-              pk[chk * 16 + ii] = pack_bf16x2(d0, d1);
-            }
+            ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], pk);
+            ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], pk + 16);
           }
           if (has_next && tid < TILE) {
             s_lse[vb ^ 1u][tid] = nl;
