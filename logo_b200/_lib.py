@@ -10,7 +10,10 @@ from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint32, c_v
 from pathlib import Path
 from typing import Optional
 
-LIB_PATH = Path(__file__).resolve().parent / "liblogo_b200.so"
+import os
+
+# LOGO_B200_LIB points at another build of the same library (e.g. one compiled with extra diagnostics)
+LIB_PATH = Path(os.environ.get("LOGO_B200_LIB") or (Path(__file__).resolve().parent / "liblogo_b200.so"))
 
 DTYPE_BF16, DTYPE_F32, DTYPE_F16, DTYPE_BOOL = 0, 1, 2, 3
 

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = uniform_warp_idx();
   const int lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
 
@@ -354,9 +354,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
   } else {
     // =====================================================================================
-    // MMA issuer
+    // MMA issuer: the whole warp walks this code, an elected lane issues (see umma_ss)
     // =====================================================================================
-    if (lane == 0) {
+    {
       const uint32_t idesc_qk = umma_idesc_bf16(TILE, TILE, 0, 0);
       const uint32_t idesc_pv = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);
       const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(128, 1)
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = uniform_warp_idx();
   AbortState ab{&abort_flag, status};
 
   if (tid == 0) {
@@ -99,12 +99,56 @@ __global__ void __launch_bounds__(128, 1)
   tc_fence_before();
   __syncthreads();
 
-  // ---- MMA ----
-  if (tid == 0) {
+  // ---- MMA: warp 0 walks the loop, an elected lane issues ----
+  if (warp == 0) {
     tc_fence_after();
     mbar_wait(&bar_load, 0, ab);
     const uint32_t a_base = smem_u32(sA);
     const uint32_t b_base = smem_u32(sB);
+    const int repeat = (args.flags >> 8) & 0xffff;   // timing mode: issue the tile product `repeat` extra times
+    const int n_cols = ((args.flags >> 4) & 1) ? 64 : 128;
+    if (repeat > 0) {
+      const long long t0 = clock64();
+      for (int rep = 0; rep < repeat; ++rep) {
+        if (args.mode == 0) {
+          const uint32_t idesc = umma_idesc_bf16(128, n_cols, 0, 0);
+#pragma unroll 1
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
+            umma_ss(tmem_d, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc, 1);
+          }
+        } else if (args.mode == 1) {
+          const uint32_t idesc = umma_idesc_bf16(128, n_cols, 0, 1);
+#pragma unroll 1
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t aoff = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
+            umma_ss(tmem_d, umma_desc_sw128(a_base + aoff, 0, 1024),
+                    umma_desc_sw128(b_base + (uint32_t)kk * args.kstep, args.lbo, args.sbo), idesc, 1);
+          }
+        } else {
+          const uint32_t idesc = umma_idesc_bf16(128, n_cols, 0, 1);
+#pragma unroll 1
+          for (int kk = 0; kk < 8; ++kk) {
+            umma_ts(tmem_d, tmem_p + (uint32_t)kk * 8u,
+                    umma_desc_sw128(b_base + (uint32_t)kk * args.kstep, args.lbo, args.sbo), idesc, 1);
+          }
+        }
+      }
+      const long long t1 = clock64();
+      umma_commit(&bar_mma);
+      mbar_wait(&bar_mma, 0, ab);
+      const long long t2 = clock64();
+      if (tid == 0 && status) {
+        status[1] = (int)(t1 - t0);   // clocks spent issuing
+        status[2] = (int)(t2 - t0);   // clocks until the last product completed
+      }
+      __syncwarp();
+      if (tid == 0) {
+        mbar_init(&bar_mma, 1);       // fresh phase for the checked product below
+        fence_barrier_init();
+      }
+      __syncwarp();
+    }
     if (args.mode == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
 #pragma unroll 1
