@@ -43,25 +43,7 @@ struct BwdArgs {
   int* status;
 };
 
-#ifdef LOGO_KERNEL_TIMING
-// Development-only phase timers (clock64 deltas summed per CTA role); compiled out by default.
-__device__ unsigned long long g_phase_clk[32];
-#define PHASE_T0() long long _pt = clock64()
-#define PHASE_ADD(slot, cond)                                             \
-  do {                                                                    \
-    const long long _now = clock64();                                     \
-    if (cond) atomicAdd(&g_phase_clk[slot], (unsigned long long)(_now - _pt)); \
-    _pt = _now;                                                           \
-  } while (0)
-#else
-#define PHASE_T0() do { } while (0)
-#define PHASE_ADD(slot, cond) do { } while (0)
-#endif
-
 constexpr int BWD_THREADS = 320;
-constexpr int QSUB = 64;                          // query rows per sub-step of the dK/dV kernel
-constexpr uint32_t SUB_BLK_BYTES = 8192;          // one [64][64] bf16 block, 128-byte swizzled
-constexpr uint32_t SUB_BYTES = 2 * SUB_BLK_BYTES;  // one [64][128] bf16 sub-tile
 constexpr int BWD_SMEM_BYTES = 6 * TILE_BYTES + 1024;
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
@@ -540,19 +522,11 @@ __device__ __forceinline__ void dkv_decode_item(const BwdArgs& a, int w, DkvItem
     first = min(it.kv_start, it.nsel);
     last = a.window > 0 ? min(it.nsel, it.kv_start + TILE + a.window) : it.nsel;
   }
-  // query rows are walked in sub-tiles of QSUB rows: [i0, i_end)
-  it.i0 = first / QSUB;
-  it.i_end = (last + QSUB - 1) / QSUB;
+  it.i0 = first / TILE;
+  it.i_end = (last + TILE - 1) / TILE;
   if (last <= first) it.i_end = it.i0;
 }
 
-// One CTA per (128-key tile, kv head). The compacted query rows that can see the tile are walked
-// in sub-tiles of 64 rows; sub-step u uses tensor-memory buffer u % 2 and shared-memory stage
-// u % 4, and the two element-wise warp groups (warps 0-3 / 4-7) take the even / odd sub-steps, so
-// while one group turns S^T into P^T and dP^T into dS^T the tensor core already works on the
-// products of the other buffer.
-//   TMEM: S^T[2] (64 cols each) | dP^T[2] (64 each) | dK (128) | dV (128)
-//   smem: K, V tiles (32 KB each) | 4 stages x (Q sub-tile 16 KB + dO sub-tile 16 KB)
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -561,16 +535,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + TILE_BYTES;
-  uint8_t* sQ = smem + 2 * TILE_BYTES;                      // 4 stages of SUB_BYTES
-  uint8_t* sDO = smem + 2 * TILE_BYTES + 4 * SUB_BYTES;     // 4 stages of SUB_BYTES
+  uint8_t* sQ = smem + 2 * TILE_BYTES;    // 2 stages
+  uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages
 
-  __shared__ uint64_t kv_full, kv_free, q_full[4], q_empty[4], do_full[4], do_empty[4];
-  __shared__ uint64_t st_full[2], dpt_full[2], p_ready[2], ds_ready[2], acc_done, epi_done;
+  __shared__ uint64_t kv_full, kv_free, q_full[2], q_empty[2], do_full[2], do_empty[2];
+  __shared__ uint64_t st_full, dpt_full, p_ready, ds_ready, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(16) float s_lse[2][2][QSUB];     // [group][buffer][row]
-  __shared__ __align__(16) float s_delta[2][2][QSUB];
-  __shared__ __align__(16) int s_pos[2][2][QSUB];
+  __shared__ __align__(16) float s_lse[2][TILE];
+  __shared__ __align__(16) float s_delta[2][TILE];
+  __shared__ __align__(16) int s_pos[2][TILE];
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
@@ -579,20 +553,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     abort_flag = 0;
     mbar_init(&kv_full, 1);
     mbar_init(&kv_free, 1);
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
       mbar_init(&do_full[s], 1);
       mbar_init(&do_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&st_full[s], 1);
-      mbar_init(&dpt_full[s], 1);
-      mbar_init(&p_ready[s], 128);
-      mbar_init(&ds_ready[s], 128);
-    }
+    mbar_init(&st_full, 1);
+    mbar_init(&dpt_full, 1);
+    mbar_init(&p_ready, 256);
+    mbar_init(&ds_ready, 256);
     mbar_init(&acc_done, 1);
-    mbar_init(&epi_done, 256);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -610,20 +581,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const int G = a.hq / a.h;
 
   if (warp < 8) {
-    const int quad = warp & 3, grp = warp >> 2;      // TMEM lane quadrant, element-wise group
-    const int gtid = tid & 127;                       // thread index inside the group
-    const int row = quad * 32 + lane;                 // key inside the tile == TMEM lane
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;   // key inside the tile
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const uint32_t tST = TM_ST + (uint32_t)grp * 64u + lane_off;
-    const uint32_t tDPT = TM_DPT + (uint32_t)grp * 64u + lane_off;
+    const int col0 = half * 64;
     const float c = a.scale_log2;
-    uint32_t u_base = 0;     // sub-steps of all previous items
-    uint32_t m = 0;          // sub-steps this group has processed
-    uint32_t n_items = 0;
+    uint32_t idx = 0, n_items = 0;
 
-    // lse / delta / position of query sub-tile `i` of head `hq` (threads 0..63 of the group)
+    // loads lse / delta / pos of query tile `i` of head `hq` into registers (threads < 128)
     auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
-      const int r = i * QSUB + gtid;
+      const int r = i * TILE + tid;
       if (r < it.nsel) {
         const size_t sidx = (size_t)hq * a.cap + it.bos_q + r;
         l = __ldg(a.lse_sel + sidx);
@@ -642,9 +609,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const int nq = it.i_end - it.i0;
       const int key_pos = it.kv_start + row;
       const bool key_valid = key_pos < it.len_k;
-      const int ecol = grp * 64;   // epilogue: this warp's 64 accumulator columns
-      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + ecol;
-      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + ecol;
+      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
       if (nq <= 0) {
         // no query can see this key tile: the gradients are zero
         if (key_valid) {
@@ -656,90 +622,74 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         continue;
       }
-      const int n_sub = nq * G;
+      const int n_steps = nq * G;
       const bool partial_keys = it.kv_start + TILE > it.len_k;
-      const int k_first = (int)((grp - (int)(u_base & 1u)) & 1);   // first sub-step of this item owned by the group
 
-      if (k_first < n_sub) {
-        if (gtid < QSUB) {
-          float l, d;
-          int pp;
-          fetch_vec(it, it.kvh * G + k_first / nq, it.i0 + k_first % nq, l, d, pp);
-          s_lse[grp][m & 1u][gtid] = l;
-          s_delta[grp][m & 1u][gtid] = d;
-          s_pos[grp][m & 1u][gtid] = pp;
-        }
-        named_barrier_sync(1 + grp, 128);
+      // vectors of the first step
+      if (tid < TILE) {
+        float l, d;
+        int p;
+        fetch_vec(it, it.kvh * G, it.i0, l, d, p);
+        s_lse[idx & 1u][tid] = l;
+        s_delta[idx & 1u][tid] = d;
+        s_pos[idx & 1u][tid] = p;
       }
+      named_barrier_sync(3, 256);
 
-      for (int k = k_first; k < n_sub; k += 2, ++m) {
-        const uint32_t vb = m & 1u;
-        // prefetch the vectors of this group's next sub-step
+      for (int s = 0; s < n_steps; ++s, ++idx) {
+        const int g = s / nq, i = it.i0 + s % nq;
+        const uint32_t vb = idx & 1u;
+        // prefetch the vectors of the next step
         float nl = 0.f, nd = 0.f;
         int np = -1;
-        const bool has_next = (k + 2 < n_sub);
-        if (has_next && gtid < QSUB) fetch_vec(it, it.kvh * G + (k + 2) / nq, it.i0 + (k + 2) % nq, nl, nd, np);
+        const bool has_next = (s + 1 < n_steps);
+        if (has_next && tid < TILE) fetch_vec(it, it.kvh * G + (s + 1) / nq, it.i0 + (s + 1) % nq, nl, nd, np);
 
-        const int pos_first = s_pos[grp][vb][0], pos_last = s_pos[grp][vb][QSUB - 1];
+        const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
                             (a.window > 0 && pos_last > it.kv_start + a.window);
         uint32_t p0[32], p1[32];
-        const bool rec = (lane == 0 && quad == 0);
-        PHASE_T0();
-        mbar_wait(&st_full[grp], m & 1u, ab);
+        mbar_wait(&st_full, idx & 1u, ab);
         tc_fence_after();
-        PHASE_ADD(0, rec);
-        tmem_ld32(tST, p0);
-        tmem_ld32(tST + 32, p1);
+        tmem_ld32(TM_ST + lane_off + (uint32_t)col0, p0);
+        tmem_ld32(TM_ST + lane_off + (uint32_t)col0 + 32, p1);
         tmem_ld_wait();
-        PHASE_ADD(1, rec);
-        prob_chunk_col(p0, c, &s_lse[grp][vb][0], &s_pos[grp][vb][0], masked, key_valid, key_pos, a.window);
-        PHASE_ADD(13, rec);
-        prob_chunk_col(p1, c, &s_lse[grp][vb][32], &s_pos[grp][vb][32], masked, key_valid, key_pos, a.window);
-        PHASE_ADD(14, rec);
+        prob_chunk_col(p0, c, &s_lse[vb][col0], &s_pos[vb][col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p1, c, &s_lse[vb][col0 + 32], &s_pos[vb][col0 + 32], masked, key_valid, key_pos, a.window);
         {
           uint32_t pk[32];
           pack_chunk(p0, pk);
           pack_chunk(p1, pk + 16);
-          PHASE_ADD(2, rec);
-          // this warp alone touches its 32 lanes of the buffer: no cross-warp hazard on the overwrite
-          tmem_st32(tST, pk);
+          named_barrier_sync(1, 256);   // all reads of S^T done before P^T overwrites it
+          tmem_st32(TM_ST + lane_off + (uint32_t)(half * 32), pk);
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(&p_ready[grp]);
-          PHASE_ADD(3, rec);
+          mbar_arrive(&p_ready);
         }
-        mbar_wait(&dpt_full[grp], m & 1u, ab);
+        mbar_wait(&dpt_full, idx & 1u, ab);
         tc_fence_after();
-        PHASE_ADD(4, rec);
         {
           uint32_t pk[32];
           {
             uint32_t d0[32], d1[32];
-            tmem_ld32(tDPT, d0);
-            tmem_ld32(tDPT + 32, d1);
+            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0, d0);
+            tmem_ld32(TM_DPT + lane_off + (uint32_t)col0 + 32, d1);
             tmem_ld_wait();
-            ds_pack_chunk_col(p0, d0, &s_delta[grp][vb][0], pk);
-            ds_pack_chunk_col(p1, d1, &s_delta[grp][vb][32], pk + 16);
+            ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], pk);
+            ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], pk + 16);
           }
-          PHASE_ADD(5, rec);
-          tmem_st32(tDPT, pk);
+          if (has_next && tid < TILE) {
+            s_lse[vb ^ 1u][tid] = nl;
+            s_delta[vb ^ 1u][tid] = nd;
+            s_pos[vb ^ 1u][tid] = np;
+          }
+          named_barrier_sync(2, 256);   // all reads of dP^T done; next step's vectors visible
+          tmem_st32(TM_DPT + lane_off + (uint32_t)(half * 32), pk);
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(&ds_ready[grp]);
-          PHASE_ADD(6, rec);
+          mbar_arrive(&ds_ready);
         }
-        if (has_next) {
-          if (gtid < QSUB) {
-            s_lse[grp][vb ^ 1u][gtid] = nl;
-            s_delta[grp][vb ^ 1u][gtid] = nd;
-            s_pos[grp][vb ^ 1u][gtid] = np;
-          }
-          named_barrier_sync(1 + grp, 128);   // the next sub-step's vectors are visible to the group
-        }
-        PHASE_ADD(7, rec);
       }
-      u_base += (uint32_t)n_sub;
 
       // ---- epilogue ----
       mbar_wait(&acc_done, n_items & 1u, ab);
@@ -747,7 +697,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       ++n_items;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)ecol;
+        const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
         const float mul = (which == 0) ? a.scale : 1.f;
         __nv_bfloat16* dst_row = (which == 0) ? dk_row : dv_row;
 #pragma unroll
@@ -770,7 +720,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
       }
       tc_fence_before();
-      mbar_arrive(&epi_done);   // the accumulators may be overwritten by the next item
     }
   } else if (warp == 8) {
     if (lane == 0) {
@@ -778,7 +727,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      uint32_t u = 0, n_items = 0;
+      uint32_t q_iter = 0, n_items = 0;
       for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
         DkvItem it;
         dkv_decode_item(a, (int)w, it);
@@ -792,17 +741,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
         tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
         ++n_items;
-        for (int k = 0; k < nq * G; ++k, ++u) {
-          const uint32_t st = u & 3u, ph = (u >> 2) & 1u;
-          const int x = (it.kvh * G + k / nq) * HEAD_DIM, y = it.bos_q + (it.i0 + k % nq) * QSUB;
+        for (int s = 0; s < nq * G; ++s, ++q_iter) {
+          const int g = s / nq, i = it.i0 + s % nq;   // query head of the group, query tile
+          const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+          const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
           mbar_wait(&q_empty[st], ph ^ 1u, ab);
-          mbar_arrive_expect_tx(&q_full[st], SUB_BYTES);
-          tma_load_2d(sQ + st * SUB_BYTES, &tm_q, &q_full[st], x, y);
-          tma_load_2d(sQ + st * SUB_BYTES + SUB_BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
+          mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
+          tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
+          tma_load_2d(sQ + st * TILE_BYTES + BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
           mbar_wait(&do_empty[st], ph ^ 1u, ab);
-          mbar_arrive_expect_tx(&do_full[st], SUB_BYTES);
-          tma_load_2d(sDO + st * SUB_BYTES, &tm_do, &do_full[st], x, y);
-          tma_load_2d(sDO + st * SUB_BYTES + SUB_BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
+          mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
+          tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
+          tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
         }
       }
       if (abort_flag) {
@@ -813,39 +763,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
   } else {
     {   // MMA issuer: the whole warp walks this code, an elected lane issues (see umma_ss)
-      const uint32_t idesc_kk = umma_idesc_bf16(TILE, QSUB, 0, 0);       // 128 x 64, both operands K-major
-      const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // 128 x 128, B operand MN-major
+      const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);
+      const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
-      uint32_t u = 0, n_items = 0;
+      uint32_t q_iter = 0, n_items = 0;
 
-      // D[128 x 64] = A[128 x 128] * B[64 x 128]^T : A a full tile, B a 64-row sub-tile
       auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
-          const uint32_t boff = (uint32_t)(kk >> 2) * SUB_BLK_BYTES + (uint32_t)(kk & 3) * 32u;
-          umma_ss(d_tmem, umma_desc_sw128(a_base + aoff, 0, 1024), umma_desc_sw128(b_base + boff, 0, 1024), idesc_kk,
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
+          umma_ss(d_tmem, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc_kk,
                   kk > 0);
         }
       };
-      // D[128 x 128] (+)= A[128 x 64 (TMEM)] * B[64 x 128 (sub-tile rows as K)]
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u,
-                  umma_desc_sw128(b_base + (uint32_t)kk * 2048u, SUB_BLK_BYTES, 1024), idesc_mn, acc || kk > 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, umma_desc_sw128(b_base + (uint32_t)kk * 2048u, BLK_BYTES, 1024),
+                  idesc_mn, acc || kk > 0);
         }
-      };
-      auto issue_scores = [&](uint32_t uu) {
-        const uint32_t st = uu & 3u, ph = (uu >> 2) & 1u, b = uu & 1u;
-        mbar_wait(&q_full[st], ph, ab);
-        tc_fence_after();
-        issue_kk(TM_ST + b * 64u, k_base, q_base + st * SUB_BYTES);
-        umma_commit(&st_full[b]);
-        mbar_wait(&do_full[st], ph, ab);
-        tc_fence_after();
-        issue_kk(TM_DPT + b * 64u, v_base, do_base + st * SUB_BYTES);
-        umma_commit(&dpt_full[b]);
       };
 
       for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
@@ -853,32 +789,45 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         dkv_decode_item(a, (int)w, it);
         const int nq = it.i_end - it.i0;
         if (nq <= 0) continue;
-        const int n_sub = nq * G;
+        const int n_steps = nq * G;
         mbar_wait(&kv_full, n_items & 1u, ab);
-        tc_fence_after();
-        issue_scores(u);
-        if (n_sub > 1) issue_scores(u + 1);
-        // the element-wise warps have read the previous item's accumulators
-        mbar_wait(&epi_done, (n_items & 1u) ^ 1u, ab);
         ++n_items;
         tc_fence_after();
-        for (int k = 0; k < n_sub; ++k, ++u) {
-          const uint32_t st = u & 3u, b = u & 1u, par = (u >> 1) & 1u;
-          PHASE_T0();
-          mbar_wait(&p_ready[b], par, ab);
+        {
+          const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+          mbar_wait(&q_full[st], ph, ab);
           tc_fence_after();
-          PHASE_ADD(8, true);
-          issue_ts(TM_DV, TM_ST + b * 64u, do_base + st * SUB_BYTES, k > 0);
+          issue_kk(TM_ST, k_base, q_base + st * TILE_BYTES);
+          umma_commit(&st_full);
+          mbar_wait(&do_full[st], ph, ab);
+          tc_fence_after();
+          issue_kk(TM_DPT, v_base, do_base + st * TILE_BYTES);
+          umma_commit(&dpt_full);
+        }
+        for (int s = 0; s < n_steps; ++s, ++q_iter) {
+          const uint32_t st = q_iter & 1u;
+          const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
+          const bool has_next = (s + 1 < n_steps);
+          mbar_wait(&p_ready, q_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DV, TM_ST, do_base + st * TILE_BYTES, s > 0);
           umma_commit(&do_empty[st]);
-          PHASE_ADD(9, true);
-          mbar_wait(&ds_ready[b], par, ab);
+          if (has_next) {
+            mbar_wait(&q_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_ST, k_base, q_base + st_n * TILE_BYTES);
+            umma_commit(&st_full);
+          }
+          mbar_wait(&ds_ready, q_iter & 1u, ab);
           tc_fence_after();
-          PHASE_ADD(10, true);
-          issue_ts(TM_DK, TM_DPT + b * 64u, q_base + st * SUB_BYTES, k > 0);
+          issue_ts(TM_DK, TM_DPT, q_base + st * TILE_BYTES, s > 0);
           umma_commit(&q_empty[st]);
-          PHASE_ADD(11, true);
-          if (k + 2 < n_sub) issue_scores(u + 2);
-          PHASE_ADD(12, true);
+          if (has_next) {
+            mbar_wait(&do_full[st_n], ph_n, ab);
+            tc_fence_after();
+            issue_kk(TM_DPT, v_base, do_base + st_n * TILE_BYTES);
+            umma_commit(&dpt_full);
+          }
         }
         umma_commit(&acc_done);
         umma_commit(&kv_free);
@@ -959,10 +908,6 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   if ((rc = make_tmap_2d_bf16(&tm_k, k, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
   if ((rc = make_tmap_2d_bf16(&tm_v, v, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
 
-  CUtensorMap tm_q64, tm_do64;   // 64-row boxes for the dK/dV kernel's sub-tiles
-  if ((rc = make_tmap_2d_bf16(&tm_q64, q_src, (uint64_t)hq * HEAD_DIM, q_rows, q_row_bytes, 64, QSUB))) return rc;
-  if ((rc = make_tmap_2d_bf16(&tm_do64, do_src, (uint64_t)hq * HEAD_DIM, q_rows, q_row_bytes, 64, QSUB))) return rc;
-
   static thread_local int attr_set_dev = -1;
   int dev = 0;
   LOGO_CHECK_CUDA(cudaGetDevice(&dev));
@@ -999,7 +944,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.status = status;
 
   prof_begin(PROF_BWD_DKV, stream);
-  attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q64, tm_do64, tm_k, tm_v, a);
+  attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
   prof_end(PROF_BWD_DKV, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_DQ, stream);
@@ -1010,17 +955,6 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
 }
 
 }  // namespace logo
-
-#ifdef LOGO_KERNEL_TIMING
-extern "C" int logo_debug_phase_clocks(unsigned long long* host_out, int n, int reset) {
-  if (host_out) cudaMemcpyFromSymbol(host_out, logo::g_phase_clk, sizeof(unsigned long long) * (size_t)(n < 32 ? n : 32));
-  if (reset) {
-    unsigned long long z[32] = {0};
-    cudaMemcpyToSymbol(logo::g_phase_clk, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 extern "C" size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered) {
   if (n_tokens < 0 || hq <= 0) return 0;
