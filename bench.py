@@ -304,6 +304,252 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------
+# secondary workloads of the same path (not the headline metric): --workload decode|fuse|layer|prefill
+# ----------------------------------------------------------------------------------------------
+def _dist_setup():
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    return dist, world, rank, device
+
+
+def _timed(fn, steps, warmup, dist, world):
+    """Device time of `steps` calls in ms (max over ranks), after `warmup` calls."""
+    for _ in range(warmup):
+        fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+
+
+def run_decode(args):
+    """One layer-step of decode attention: 16 sequences x 32768 cached tokens per 96 GiB of cache
+    (the 1-GPU point of the 64-sequence configuration), Bernoulli(0.5) active sequences, KV heads
+    sharded over the ranks. Reports achieved HBM GB/s on the algorithmic bytes."""
+    from logo_b200 import Cache
+    from logo_b200.layers import decode_attention
+
+    dist, world, rank, device = _dist_setup()
+    peaks = measured_peaks()
+    B, ctx, heads, window = args.decode_batch, 32768, 16 // world, 128
+    g = torch.Generator(device=device).manual_seed(7)
+    mk = lambda *sh: torch.randn(*sh, device=device, generator=g).to(torch.bfloat16)
+    cache = Cache(max_length=ctx + 8)
+    chunk = 4096
+    for _ in range(ctx // chunk):   # fill the cache in chunks to bound the staging memory
+        cache.append(0, mk(B, chunk, heads, D), mk(B, chunk, heads, D), mk(B, chunk, heads, D), mk(B, chunk, heads, D),
+                     window)
+    st = cache.layer_buffers(0)
+    ql, qg = mk(B, heads, D), mk(B, heads, D)
+    gate = torch.rand(B, device=device, generator=torch.Generator(device=device).manual_seed(11)).to(torch.bfloat16)
+    thres = torch.tensor([0.5], device=device)
+    n_active = int((gate.float() >= 0.5).sum().item())
+    bytes_step = (n_active * 2 * ctx + B * 2 * min(ctx, window + 1)) * heads * D * 2 + 4 * B * heads * D * 2
+    ms = _timed(lambda: decode_attention(ql, qg, st, gate, thres, SCALE), args.steps, args.warmup, dist, world)
+    if rank == 0:
+        gbs = bytes_step * world * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"decode attention, one layer-step, B={B}, ctx={ctx}, {16} kv heads sharded over "
+                                   f"{world} rank(s), {n_active}/{B} sequences active", "bytes_per_step": bytes_step * world},
+            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": gbs / world, "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": gbs / world / peaks["hbm"], "traffic": None,
+                         "peak_source": f"{peaks['source']} copy bandwidth"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_fuse(args):
+    """Fused RMSNorm + gate blend, forward and backward, 32768 tokens x 16 heads, ratio as given."""
+    from logo_b200 import _lib
+
+    dist, world, rank, device = _dist_setup()
+    peaks = measured_peaks()
+    lib = _lib.load()
+    n, h = N_TOK, HQ
+    g = torch.Generator(device=device).manual_seed(3)
+    mk = lambda *sh: torch.randn(*sh, device=device, generator=g).to(torch.bfloat16)
+    local, glob, d_out = mk(n, h, D), mk(n, h, D), mk(n, h * D)
+    gate = torch.rand(n, device=device, generator=g).to(torch.bfloat16)
+    thres = torch.tensor([1.0 - args.ratio], device=device)
+    wl, wg = mk(D) * 0.1 + 1, mk(D) * 0.1 + 1
+    out, d_local, d_glob, d_gate = torch.empty_like(d_out), torch.empty_like(local), torch.empty_like(glob), \
+        torch.empty_like(gate)
+    d_wl, d_wg = torch.empty_like(wl), torch.empty_like(wg)
+    ws = torch.empty(lib.logo_fuse_bwd_workspace_bytes(n), dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device).cuda_stream
+    sq = int((gate.float() >= thres.item()).sum().item())
+
+    def fwd():
+        _lib.check(lib.logo_fuse_fwd(local.data_ptr(), glob.data_ptr(), gate.data_ptr(), 0, thres.data_ptr(), 1,
+                                     wl.data_ptr(), wg.data_ptr(), 0, out.data_ptr(), n, h, D, 1e-5, 1, stream), "fuse")
+
+    def bwd():
+        _lib.check(lib.logo_fuse_bwd(d_out.data_ptr(), local.data_ptr(), glob.data_ptr(), gate.data_ptr(), 0,
+                                     thres.data_ptr(), 1, wl.data_ptr(), wg.data_ptr(), 0, d_local.data_ptr(),
+                                     d_glob.data_ptr(), d_gate.data_ptr(), d_wl.data_ptr(), d_wg.data_ptr(), n, h, D,
+                                     1e-5, 1, ws.data_ptr(), ws.numel(), stream), "fuse bwd")
+
+    row = h * D * 2
+    bytes_fwd = (2 * n + sq) * row + 2 * n
+    bytes_bwd = (4 * n + 2 * sq) * row + 4 * n        # reads d_out, local, glob(sel); writes d_local, d_glob
+    ms_f = _timed(fwd, args.steps, args.warmup, dist, world)
+    ms_b = _timed(bwd, args.steps, args.warmup, dist, world)
+    if rank == 0:
+        gf = bytes_fwd * args.steps / (ms_f * 1e-3) / 1e9
+        gb = bytes_bwd * args.steps / (ms_b * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "fuse_fwd_hbm_gbs", "value": gf, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_f / args.steps, "higher_is_better": True, "scaling": "weak",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"fused RMSNorm + gate blend, {n} tokens x {h} heads, {sq} selected",
+                       "bytes_fwd": bytes_fwd, "bytes_bwd": bytes_bwd},
+            "backward": {"value": gb, "unit": "GB/s", "ms_per_step": ms_b / args.steps, "frac": gb / peaks["hbm"]},
+            "roofline": {"bound": "hbm", "kernel": "fuse_fwd_kernel", "achieved": gf, "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": gf / peaks["hbm"], "traffic": None,
+                         "peak_source": f"{peaks['source']} copy bandwidth"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _varlen_lengths(total, count, lo, hi, seed):
+    rs = np.random.RandomState(seed)
+    raw = rs.uniform(lo, hi, count)
+    lens = np.maximum((raw / raw.sum() * total).astype(np.int64), 1)
+    lens[-1] += total - lens.sum()
+    return lens.tolist()
+
+
+def run_layer(args):
+    """Training step (forward + backward) of one LoGo attention layer: 8 packed sequences with
+    lengths ~U[512, 8192] summing to 32768 tokens, hidden 2048, 16 x 128, global ratio 0.25.
+    With N ranks the sequences are dealt to the ranks (longest first), weights replicated."""
+    from logo_b200 import LoGoAttention
+    from logo_b200.config import LoGoConfig
+
+    dist, world, rank, device = _dist_setup()
+    lens = sorted(_varlen_lengths(N_TOK, 8, 512, 8192, 5), reverse=True)
+    mine = [l for i, l in enumerate(lens) if i % world == rank] if world > 1 else lens
+    cfg = LoGoConfig(hidden_size=2048, num_attention_heads=16, num_key_value_heads=16, window_size=128,
+                     global_qk_param="linear_proj", num_hidden_layers=1, rms_norm_eps=1e-5,
+                     max_position_embeddings=8192)
+    torch.manual_seed(0)
+    layer = LoGoAttention(cfg, 0).to(device=device, dtype=torch.bfloat16).train()
+    n = sum(mine)
+    g = torch.Generator(device=device).manual_seed(1 + rank)
+    hidden = torch.randn(1, n, 2048, device=device, generator=g).to(torch.bfloat16).requires_grad_(True)
+    d_out = torch.randn(1, n, 2048, device=device, generator=g).to(torch.bfloat16)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(mine)]), dtype=torch.int32, device=device)
+    pos = torch.cat([torch.arange(l, device=device) for l in mine])[None]
+    with torch.no_grad():   # threshold at the 75th percentile of the gates: 25 % of the tokens go global
+        gate = torch.sigmoid(layer.gate_proj(hidden)).float().flatten()
+        layer.gate_thres.fill_(torch.quantile(gate, 0.75).item())
+
+    def step():
+        hidden.grad = None
+        out, _, _ = layer(hidden, position_ids=pos, cu_seqlens=cu)
+        out.backward(d_out)
+
+    ms = _timed(step, args.steps, args.warmup, dist, world)
+    if rank == 0:
+        tps = N_TOK * args.steps / (ms * 1e-3)
+        print(json.dumps({
+            "metric": "logo_layer_train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "LoGo attention layer fwd+bwd, 8 packed sequences (lengths " + str(lens) +
+                                   "), hidden 2048, 16x128, window 128, global ratio 0.25"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_prefill(args):
+    """Prefill of a 24-layer, hidden-2048 LoGo decoder stack (the 1.5B configuration with vocabulary
+    32000): the attention layers are this package's, the rest (embedding, RMSNorm, SwiGLU MLP 5632,
+    lm_head on the last token) is plain torch. B = 8 x 8192 tokens, batch-sharded over the ranks,
+    gate threshold 0.5. Random bf16 weights."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from logo_b200 import LoGoAttention
+    from logo_b200.config import LoGoConfig
+    from logo_b200.layers import RMSNorm
+
+    dist, world, rank, device = _dist_setup()
+    cfg = LoGoConfig(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=24,
+                     num_attention_heads=16, num_key_value_heads=16, window_size=128, global_qk_param="linear_proj",
+                     gate_thres_init=0.5, rms_norm_eps=1e-5, max_position_embeddings=8192)
+
+    class Block(nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            self.ln1, self.ln2 = RMSNorm(2048, 1e-5), RMSNorm(2048, 1e-5)
+            self.attn = LoGoAttention(cfg, i)
+            self.gate_up = nn.Linear(2048, 2 * 5632, bias=False)
+            self.down = nn.Linear(5632, 2048, bias=False)
+
+        def forward(self, x, pos_emb, pos):
+            x = x + self.attn(self.ln1(x), position_ids=pos, position_embeddings=pos_emb)[0]
+            gu = self.gate_up(self.ln2(x))
+            a, b = gu.chunk(2, dim=-1)
+            return x + self.down(F.silu(a) * b)
+
+    torch.manual_seed(0)
+    emb = nn.Embedding(32000, 2048)
+    blocks = nn.ModuleList([Block(i) for i in range(24)])
+    for m in list(blocks.modules()) + [emb]:
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, std=0.02)
+    emb, blocks = emb.to(device, torch.bfloat16), blocks.to(device, torch.bfloat16).eval()
+    norm_f = RMSNorm(2048, 1e-5).to(device, torch.bfloat16)
+    b_local, t = 8 // world, 8192
+    ids = torch.randint(0, 32000, (b_local, t), device=device, generator=torch.Generator(device=device).manual_seed(rank))
+    pos = torch.arange(t, device=device)[None].expand(b_local, -1)
+
+    @torch.no_grad()
+    def step():
+        x = emb(ids)
+        pos_emb = blocks[0].attn.rotary_emb(x, pos)
+        for blk in blocks:
+            x = blk(x, pos_emb, pos)
+        return F.linear(norm_f(x[:, -1]), emb.weight)
+
+    ms = _timed(step, args.steps, args.warmup, dist, world)
+    if rank == 0:
+        tps = 8 * t * args.steps / (ms * 1e-3)
+        print(json.dumps({
+            "metric": "logo_1b5_prefill_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "24-layer LoGo decoder stack prefill, 8 x 8192 tokens, hidden 2048, MLP 5632, "
+                                   "vocab 32000, gate threshold 0.5; attention layers from this package, the rest torch"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -330,6 +576,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ratio", type=float, default=0.5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "fuse", "layer", "prefill"],
+                    help="sq_attn is the headline metric; the others measure further rows of the same path")
+    ap.add_argument("--decode-batch", type=int, default=16)
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: leave out the CPU baseline leg")
     args = ap.parse_args()
@@ -337,8 +586,10 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    else:
+    elif args.workload == "sq_attn":
         run_gpu(args)
+    else:
+        {"decode": run_decode, "fuse": run_fuse, "layer": run_layer, "prefill": run_prefill}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -22,6 +22,7 @@ namespace logo {
 
 constexpr int FUSE_THREADS = 256;
 constexpr int FUSE_D = 128;
+constexpr int FUSE_U = 4;   // head pairs whose loads are in flight together (forward)
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
@@ -111,28 +112,41 @@ __global__ void __launch_bounds__(FUSE_THREADS)
     const bool selected = gate_f >= thres;
     const float g = selected ? gate_f : 0.f;
     const float one_minus_g = bf16_round(1.f - g);
-    for (int hb = 0; hb < h; hb += 2) {   // uniform trip count: the row sums shuffle across the full warp
-      const int hh = hb + sub;
-      const bool act = hh < h;
-      const size_t off = ((size_t)tok * h + (act ? hh : 0)) * FUSE_D + col;
-      float x[8], xh[8], yl[8], res[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(local + off)), x);
-      normalise8(x, eps, use_norm != 0, xh);
+    // FUSE_U head pairs per iteration: all their loads are issued before the first reduction, which
+    // is what keeps enough bytes in flight. The trip count is warp-uniform (the row sums shuffle).
+    for (int hb = 0; hb < h; hb += 2 * FUSE_U) {
+      uint4 lv[FUSE_U], gv[FUSE_U];
+      size_t off[FUSE_U];
+      bool act[FUSE_U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) yl[i] = (use_norm && bf16_w) ? bf16_round(wl[i] * xh[i]) : wl[i] * xh[i];
-      if (selected) {
-        float yg[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(glob + off)), x);
+      for (int u = 0; u < FUSE_U; ++u) {
+        const int hh = hb + 2 * u + sub;
+        act[u] = hh < h;
+        off[u] = ((size_t)tok * h + (act[u] ? hh : 0)) * FUSE_D + col;
+        lv[u] = __ldg(reinterpret_cast<const uint4*>(local + off[u]));
+        if (selected) gv[u] = __ldg(reinterpret_cast<const uint4*>(glob + off[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < FUSE_U; ++u) {
+        float x[8], xh[8], yl[8], res[8];
+        unpack8(lv[u], x);
         normalise8(x, eps, use_norm != 0, xh);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) yg[i] = (use_norm && bf16_w) ? bf16_round(wg[i] * xh[i]) : wg[i] * xh[i];
+        for (int i = 0; i < 8; ++i) yl[i] = (use_norm && bf16_w) ? bf16_round(wl[i] * xh[i]) : wl[i] * xh[i];
+        if (selected) {
+          float yg[8];
+          unpack8(gv[u], x);
+          normalise8(x, eps, use_norm != 0, xh);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) res[i] = bf16_round(one_minus_g * yl[i]) + bf16_round(g * yg[i]);
-      } else {
+          for (int i = 0; i < 8; ++i) yg[i] = (use_norm && bf16_w) ? bf16_round(wg[i] * xh[i]) : wg[i] * xh[i];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) res[i] = yl[i];
+          for (int i = 0; i < 8; ++i) res[i] = bf16_round(one_minus_g * yl[i]) + bf16_round(g * yg[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) res[i] = yl[i];
+        }
+        if (act[u]) *reinterpret_cast<uint4*>(out + off[u]) = pack8(res);
       }
-      if (act) *reinterpret_cast<uint4*>(out + off) = pack8(res);
     }
   }
 }
@@ -166,19 +180,25 @@ __global__ void __launch_bounds__(FUSE_THREADS)
     const float g = selected ? gate_f : 0.f;
     const float one_minus_g = 1.f - g;
     float dgate = 0.f;
+#pragma unroll 2
     for (int hb = 0; hb < h; hb += 2) {
       const int hh = hb + sub;
       const bool act = hh < h;
       const size_t off = ((size_t)tok * h + (act ? hh : 0)) * FUSE_D + col;
       float go[8], x[8], xh[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(d_out + off)), go);
+      // all three loads of the row are issued before the first reduction
+      const uint4 go_v = __ldg(reinterpret_cast<const uint4*>(d_out + off));
+      const uint4 lo_v = __ldg(reinterpret_cast<const uint4*>(local + off));
+      uint4 gl_v = make_uint4(0, 0, 0, 0);
+      if (selected) gl_v = __ldg(reinterpret_cast<const uint4*>(glob + off));
+      unpack8(go_v, go);
       if (!act) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) go[i] = 0.f;
       }
 
       // local branch
-      unpack8(__ldg(reinterpret_cast<const uint4*>(local + off)), x);
+      unpack8(lo_v, x);
       const float rstd_l = normalise8(x, eps, use_norm != 0, xh);
       float dxh[8], dot = 0.f, res[8];
 #pragma unroll
@@ -201,7 +221,7 @@ __global__ void __launch_bounds__(FUSE_THREADS)
 
       // global branch
       if (selected) {
-        unpack8(__ldg(reinterpret_cast<const uint4*>(glob + off)), x);
+        unpack8(gl_v, x);
         const float rstd_g = normalise8(x, eps, use_norm != 0, xh);
         dot = 0.f;
 #pragma unroll
