@@ -54,6 +54,15 @@ enum {
 /* Query-tile height of the attention kernels (compacted rows per tile). */
 #define LOGO_TILE 128
 
+/* Size of the `meta` buffer and the slots the attention kernels use in it. */
+#define LOGO_META_INTS 16
+#define LOGO_META_COUNTER_SQ_FWD 8
+#define LOGO_META_COUNTER_SWA_FWD 9
+#define LOGO_META_COUNTER_SQ_DKV 10
+#define LOGO_META_COUNTER_SQ_DQ 11
+#define LOGO_META_COUNTER_SWA_DKV 12
+#define LOGO_META_COUNTER_SWA_DQ 13
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int logo_version(void);
 
@@ -79,7 +88,10 @@ int logo_last_error(char* buf, int n);
  *                row 1: ceil(sequence length / 128)                (key tiles, backward)
  *                row 2: ceil(sequence length / 256)                (query-tile pairs, local branch)
  *                row 3: ceil(selected rows of the sequence / 128)  (query tiles, backward)
- *   meta         [8] int32: [0] Sq, [1..4] totals of rows 0..3, rest 0
+ *   meta         [LOGO_META_INTS] int32: [0] Sq, [1..4] totals of rows 0..3, [5..7] 0; entries 8..15 are
+ *                scratch of the attention kernels (their work-claim counters, reset at every launch):
+ *                two launches of the same attention entry point that share one meta buffer must not
+ *                overlap on the GPU
  *   gate_sum     [1] fp32, sum of float(gate) over all rows (0 for BOOL); may be NULL
  *   workspace    logo_select_workspace_bytes(n_tokens) bytes, 16-byte aligned
  * Nothing is copied to the host: Sq stays on the device, so q_idx / pos_ids are sized for n_tokens.
@@ -133,7 +145,7 @@ int logo_select_rows_static(const void* gate, int gate_dtype, const void* thres,
  * ------------------------------------------------------------------------------------------ */
 int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int64_t* q_idx,
                      const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                     const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
+                     const int32_t* tile_off, int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
                      float scale, int zero_fill, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -143,7 +155,7 @@ int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float
  *   tile_off, meta: outputs of logo_select_rows for the same cu_seqlens (rows 2 / entry 3 are used)
  * ------------------------------------------------------------------------------------------ */
 int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* cu_seqlens,
-                 const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
+                 const int32_t* tile_off, int32_t* meta, int n_seq, int n_tokens, int hq, int h, int d,
                  int window, float scale, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -166,12 +178,12 @@ size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered);
 int logo_sq_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                      void* dq, void* dk, void* dv, const int64_t* q_idx, const int32_t* pos_ids,
                      const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* tile_off,
-                     const int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq,
+                     int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq,
                      int h, int d, float scale, int32_t* status, logo_stream_t stream);
 
 int logo_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                  void* dq, void* dk, void* dv, const int32_t* cu_seqlens, const int32_t* tile_off,
-                 const int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq, int h,
+                 int32_t* meta, void* workspace, size_t workspace_bytes, int n_seq, int n_tokens, int hq, int h,
                  int d, int window, float scale, int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

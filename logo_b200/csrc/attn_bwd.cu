@@ -32,6 +32,8 @@ struct BwdArgs {
   const int32_t* n_qtiles;
   const int32_t* tile_off_k;  // [n_seq+1] prefix of 128-key tiles
   const int32_t* n_ktiles;
+  int* counter_dq;            // [1] zeroed before the launch: next unclaimed item of the dQ kernel
+  int* counter_dkv;           // [1] same for the dK/dV kernel
   const float* lse_sel;       // [hq][cap] head-major, compact rows
   const float* delta_sel;     // [hq][cap]
   int cap;
@@ -258,6 +260,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __shared__ uint64_t s_full[2], dp_full, ds_ready, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int s_items[ITEM_RING];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
@@ -276,6 +281,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     mbar_init(&dp_full, 1);
     mbar_init(&ds_ready, 256);
     mbar_init(&acc_done, 1);
+    ring_init(ring);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -300,10 +306,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     uint32_t idx = 0;      // key steps processed so far (all items)
     uint32_t n_items = 0;
 
-    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+    for (uint32_t n_ring = 0;; ++n_ring) {
+      const long long w = ring_pop(ring, n_ring, ab);
+      if (w < 0) break;
       DqItem it;
       dq_decode_item(a, (int)w, total_tiles, it);
-      if (it.nrows == 0) continue;
+      if (it.nrows == 0) {
+        ring_release(ring, n_ring);
+        continue;
+      }
       const int rowv = min(row, it.nrows - 1);
       const int my_pos = bwd_row_position(a, it.bos_q, it.r_base + rowv);
       const size_t sidx = (size_t)it.hq * a.cap + it.bos_q + it.r_base + rowv;
@@ -371,6 +382,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
       }
       tc_fence_before();
+      ring_release(ring, n_ring);
     }
   } else if (warp == 8) {
     if (lane == 0) {
@@ -379,7 +391,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       uint32_t kv_iter = 0, n_items = 0;
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_push(ring, n_ring, a.counter_dq, total_items, ab);
+        if (w < 0) break;
         DqItem it;
         dq_decode_item(a, (int)w, total_tiles, it);
         if (it.nrows == 0) continue;
@@ -434,10 +448,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
       };
 
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_pop(ring, n_ring, ab);
+        if (w < 0) break;
         DqItem it;
         dq_decode_item(a, (int)w, total_tiles, it);
-        if (it.nrows == 0) continue;
+        if (it.nrows == 0) {
+          ring_release(ring, n_ring);
+          continue;
+        }
         mbar_wait(&qdo_full, n_items & 1u, ab);
         ++n_items;
         tc_fence_after();
@@ -477,6 +496,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         umma_commit(&acc_done);
         umma_commit(&qdo_free);
+        ring_release(ring, n_ring);
       }
     }
   }
@@ -545,6 +565,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __shared__ __align__(16) float s_lse[2][TILE];
   __shared__ __align__(16) float s_delta[2][TILE];
   __shared__ __align__(16) int s_pos[2][TILE];
+  __shared__ int s_items[ITEM_RING];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
@@ -564,6 +587,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     mbar_init(&p_ready, 256);
     mbar_init(&ds_ready, 256);
     mbar_init(&acc_done, 1);
+    ring_init(ring);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -603,7 +627,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       }
     };
 
-    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+    for (uint32_t n_ring = 0;; ++n_ring) {
+      const long long w = ring_pop(ring, n_ring, ab);
+      if (w < 0) break;
       DkvItem it;
       dkv_decode_item(a, (int)w, it);
       const int nq = it.i_end - it.i0;
@@ -620,6 +646,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             reinterpret_cast<uint4*>(dv_row)[g] = make_uint4(0, 0, 0, 0);
           }
         }
+        ring_release(ring, n_ring);
         continue;
       }
       const int n_steps = nq * G;
@@ -720,6 +747,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
       }
       tc_fence_before();
+      ring_release(ring, n_ring);
     }
   } else if (warp == 8) {
     if (lane == 0) {
@@ -728,7 +756,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       uint32_t q_iter = 0, n_items = 0;
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_push(ring, n_ring, a.counter_dkv, total_items, ab);
+        if (w < 0) break;
         DkvItem it;
         dkv_decode_item(a, (int)w, it);
         const int nq = it.i_end - it.i0;
@@ -784,11 +814,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
       };
 
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_pop(ring, n_ring, ab);
+        if (w < 0) break;
         DkvItem it;
         dkv_decode_item(a, (int)w, it);
         const int nq = it.i_end - it.i0;
-        if (nq <= 0) continue;
+        if (nq <= 0) {
+          ring_release(ring, n_ring);
+          continue;
+        }
         const int n_steps = nq * G;
         mbar_wait(&kv_full, n_items & 1u, ab);
         ++n_items;
@@ -831,6 +866,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         umma_commit(&acc_done);
         umma_commit(&kv_free);
+        ring_release(ring, n_ring);
       }
     }
   }
@@ -877,7 +913,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
                            const void* d_o, void* dq, void* dk, void* dv, const int64_t* q_idx,
                            const int32_t* pos_ids, const int32_t* cu_q, const int32_t* cu_k, const int32_t* tile_off_q,
                            const int32_t* n_qtiles, const int32_t* tile_off_k, const int32_t* n_ktiles,
-                           const int32_t* sq_ptr, int n_seq, int n_tokens, int hq, int h, int window, float scale,
+                           const int32_t* sq_ptr, int* counter_dq, int* counter_dkv, int n_seq, int n_tokens, int hq, int h, int window, float scale,
                            void* workspace, size_t workspace_bytes, int32_t* status, cudaStream_t stream) {
   const bool gathered = (q_idx != nullptr);
   BwdWorkspace ws = bwd_workspace_layout(workspace, n_tokens, hq, gathered);
@@ -928,6 +964,8 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.n_qtiles = n_qtiles;
   a.tile_off_k = tile_off_k;
   a.n_ktiles = n_ktiles;
+  a.counter_dq = counter_dq;
+  a.counter_dkv = counter_dkv;
   a.lse_sel = ws.lse_sel;
   a.delta_sel = ws.delta_sel;
   a.cap = ws.cap;
@@ -943,6 +981,8 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
 
+  LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dq, 0, sizeof(int), stream));
+  LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dkv, 0, sizeof(int), stream));
   prof_begin(PROF_BWD_DKV, stream);
   attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
   prof_end(PROF_BWD_DKV, stream);
@@ -964,7 +1004,7 @@ extern "C" size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gather
 extern "C" int logo_sq_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                                 const void* d_o, void* dq, void* dk, void* dv, const int64_t* q_idx,
                                 const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                const int32_t* tile_off, const int32_t* meta, void* workspace, size_t workspace_bytes,
+                                const int32_t* tile_off, int32_t* meta, void* workspace, size_t workspace_bytes,
                                 int n_seq, int n_tokens, int hq, int h, int d, float scale, int32_t* status,
                                 logo_stream_t stream) {
   using namespace logo;
@@ -979,13 +1019,13 @@ extern "C" int logo_sq_attn_bwd(const void* q, const void* k, const void* v, con
                    aligned16(dk) && aligned16(dv),
                LOGO_ERR_INVALID, "tensors must be 16-byte aligned");
   return launch_attn_bwd(q, k, v, o, lse, d_o, dq, dk, dv, q_idx, pos_ids, cu_seqlens_q, cu_seqlens_k,
-                         tile_off + 3 * (n_seq + 1), meta + 4, tile_off + (n_seq + 1), meta + 2, meta, n_seq, n_tokens,
-                         hq, h, 0, scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
+                         tile_off + 3 * (n_seq + 1), meta + 4, tile_off + (n_seq + 1), meta + 2, meta,
+                         meta + LOGO_META_COUNTER_SQ_DQ, meta + LOGO_META_COUNTER_SQ_DKV, n_seq, n_tokens, hq, h, 0, scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
 }
 
 extern "C" int logo_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                             const void* d_o, void* dq, void* dk, void* dv, const int32_t* cu_seqlens,
-                            const int32_t* tile_off, const int32_t* meta, void* workspace, size_t workspace_bytes,
+                            const int32_t* tile_off, int32_t* meta, void* workspace, size_t workspace_bytes,
                             int n_seq, int n_tokens, int hq, int h, int d, int window, float scale, int32_t* status,
                             logo_stream_t stream) {
   using namespace logo;
@@ -1001,6 +1041,7 @@ extern "C" int logo_swa_bwd(const void* q, const void* k, const void* v, const v
                LOGO_ERR_INVALID, "tensors must be 16-byte aligned");
   // identity selection: query tiles == key tiles (row 1 of tile_off, meta[2])
   return launch_attn_bwd(q, k, v, o, lse, d_o, dq, dk, dv, nullptr, nullptr, cu_seqlens, cu_seqlens,
-                         tile_off + (n_seq + 1), meta + 2, tile_off + (n_seq + 1), meta + 2, nullptr, n_seq, n_tokens,
-                         hq, h, window, scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
+                         tile_off + (n_seq + 1), meta + 2, tile_off + (n_seq + 1), meta + 2, nullptr,
+                         meta + LOGO_META_COUNTER_SWA_DQ, meta + LOGO_META_COUNTER_SWA_DKV, n_seq, n_tokens, hq, h, window,
+                         scale, workspace, workspace_bytes, status, (cudaStream_t)stream);
 }

@@ -35,6 +35,7 @@ struct AttnArgs {
   const int32_t* cu_k;       // [n_seq + 1] token prefix per sequence
   const int32_t* tile_off;   // [n_seq + 1] prefix of work tiles per sequence (unit depends on the kernel)
   const int32_t* n_tiles;    // [1] total number of work tiles
+  int* work_counter;         // [1] zeroed before the launch: the next unclaimed work item
   int n_seq;
   int n_tokens;
   int hq;
@@ -54,6 +55,54 @@ __device__ __forceinline__ int find_sequence(const int32_t* __restrict__ off, in
     if (__ldg(off + mid) <= x) lo = mid; else hi = mid;
   }
   return lo;
+}
+
+// Work distribution. Items (tile, head) are listed heaviest-first per sequence and claimed
+// dynamically from a global counter, so CTAs that drew light items simply take more of them (a
+// static round-robin leaves 10-60 % of the SMs idle at the tail; sorting all items by cost instead
+// balances as well but scatters concurrent CTAs over the K/V streams and costs more in L2 misses
+// than it gains). One thread of the producer warp claims items and publishes them through a small
+// shared-memory ring; the MMA warp and the eight element-wise warps consume them in order.
+constexpr int ITEM_RING = 4;
+constexpr int ITEM_CONSUMER_WARPS = 9;
+
+struct ItemRing {
+  volatile int* items;   // [ITEM_RING]
+  uint64_t* full;        // [ITEM_RING] count 1
+  uint64_t* empty;       // [ITEM_RING] count ITEM_CONSUMER_WARPS
+};
+
+__device__ __forceinline__ void ring_init(const ItemRing& r) {
+  for (int i = 0; i < ITEM_RING; ++i) {
+    mbar_init(&r.full[i], 1);
+    mbar_init(&r.empty[i], ITEM_CONSUMER_WARPS);
+  }
+}
+
+// Producer (one thread): claim item number `n` of this CTA. Returns the item, or -1 when the list
+// is exhausted; the -1 is published as well so that the consumers stop.
+__device__ __forceinline__ long long ring_push(const ItemRing& r, uint32_t n, int* counter, long long total,
+                                               const AbortState& ab) {
+  const uint32_t slot = n % ITEM_RING, ph = (n / ITEM_RING) & 1u;
+  mbar_wait(&r.empty[slot], ph ^ 1u, ab);
+  long long w = (long long)atomicAdd(counter, 1);
+  if (w >= total || *ab.smem_abort) w = -1;
+  r.items[slot] = (int)w;
+  mbar_arrive(&r.full[slot]);
+  return w;
+}
+
+// Consumer (every thread of the role): the n-th item of this CTA, or -1.
+__device__ __forceinline__ long long ring_pop(const ItemRing& r, uint32_t n, const AbortState& ab) {
+  const uint32_t slot = n % ITEM_RING, ph = (n / ITEM_RING) & 1u;
+  if (!mbar_wait(&r.full[slot], ph, ab)) return -1;
+  return (long long)r.items[slot];
+}
+
+// Consumer: the calling WARP is done with item `n` (call from all lanes; one arrives).
+__device__ __forceinline__ void ring_release(const ItemRing& r, uint32_t n) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(&r.empty[n % ITEM_RING]);
 }
 
 // Position of compacted row `r` (relative to the start of the sequence's compacted rows).

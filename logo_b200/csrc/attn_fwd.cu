@@ -124,6 +124,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   __shared__ uint64_t q_ready[2], s_full[2], p_ready[2], o_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int s_items[ITEM_RING];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
 
   const int tid = threadIdx.x;
   const int warp = uniform_warp_idx();
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&p_ready[t], TILE);
       mbar_init(&o_done[t], 1);
     }
+    ring_init(ring);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -172,11 +176,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     uint32_t n_steps = 0;   // (tile, key-step) pairs processed so far == S / P / O barrier phases
     uint32_t n_items = 0;   // items in which this tile was active
 
-    for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+    for (uint32_t n_ring = 0;; ++n_ring) {
+      const long long w = ring_pop(ring, n_ring, ab);
+      if (w < 0) break;
       FwdItem it;
       fwd_decode_item(a, (int)w, total_pairs, it);
       const int nrows = it.nrows[t];
-      if (nrows == 0) continue;
+      if (nrows == 0) {
+        ring_release(ring, n_ring);
+        continue;
+      }
       const int r_base = it.row0 + t * TILE;
 
       // ---- gather the query rows into swizzled shared memory ----
@@ -317,6 +326,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       if (store && a.lse) a.lse[(size_t)tok * a.hq + it.hq] = m_run * c + log2f(l_run);
       tc_fence_before();
+      ring_release(ring, n_ring);
     }
   } else if (warp == 8) {
     // =====================================================================================
@@ -326,7 +336,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       uint32_t kv_iter = 0;
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_push(ring, n_ring, a.work_counter, total_items, ab);
+        if (w < 0) break;
         FwdItem it;
         fwd_decode_item(a, (int)w, total_pairs, it);
         const int x = it.kvh * HEAD_DIM;
@@ -384,10 +396,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         umma_commit(&o_done[t]);
       };
 
-      for (long long w = blockIdx.x; w < total_items; w += gridDim.x) {
+      for (uint32_t n_ring = 0;; ++n_ring) {
+        const long long w = ring_pop(ring, n_ring, ab);
+        if (w < 0) break;
         FwdItem it;
         fwd_decode_item(a, (int)w, total_pairs, it);
-        if (it.JE <= it.JB) continue;
+        if (it.JE <= it.JB) {
+          ring_release(ring, n_ring);
+          continue;
+        }
         for (int t = 0; t < 2; ++t) {
           if (it.nrows[t] > 0) {
             mbar_wait(&q_ready[t], n_items[t] & 1u, ab);
@@ -430,6 +447,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             }
           }
         }
+        ring_release(ring, n_ring);
       }
     }
   }
@@ -454,6 +472,7 @@ static int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     attr_set_dev = dev;
   }
   const int grid = sm_count();
+  LOGO_CHECK_CUDA(cudaMemsetAsync(a.work_counter, 0, sizeof(int), stream));
   prof_begin(PROF_ATTN_FWD, stream);
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tm_k, tm_v, a);
   prof_end(PROF_ATTN_FWD, stream);
@@ -476,7 +495,7 @@ static int check_attn_common(const void* q, const void* k, const void* v, const 
 
 extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int64_t* q_idx,
                                 const int32_t* pos_ids, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                const int32_t* tile_off, const int32_t* meta, int n_seq, int n_tokens, int hq, int h,
+                                const int32_t* tile_off, int32_t* meta, int n_seq, int n_tokens, int hq, int h,
                                 int d, float scale, int zero_fill, int32_t* status, logo_stream_t stream_) {
   using namespace logo;
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -499,6 +518,7 @@ extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, voi
   a.cu_k = cu_seqlens_k;
   a.tile_off = tile_off;  // row 0: selected-row pairs
   a.n_tiles = meta + 1;
+  a.work_counter = meta + LOGO_META_COUNTER_SQ_FWD;
   a.n_seq = n_seq;
   a.n_tokens = n_tokens;
   a.hq = hq;
@@ -511,7 +531,7 @@ extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, voi
 }
 
 extern "C" int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
-                            const int32_t* cu_seqlens, const int32_t* tile_off, const int32_t* meta, int n_seq,
+                            const int32_t* cu_seqlens, const int32_t* tile_off, int32_t* meta, int n_seq,
                             int n_tokens, int hq, int h, int d, int window, float scale, int32_t* status,
                             logo_stream_t stream_) {
   using namespace logo;
@@ -533,6 +553,7 @@ extern "C" int logo_swa_fwd(const void* q, const void* k, const void* v, void* o
   a.cu_k = cu_seqlens;
   a.tile_off = tile_off + 2 * (n_seq + 1);  // row 2: all-row pairs
   a.n_tiles = meta + 3;
+  a.work_counter = meta + LOGO_META_COUNTER_SWA_FWD;
   a.n_seq = n_seq;
   a.n_tokens = n_tokens;
   a.hq = hq;

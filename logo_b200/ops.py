@@ -86,7 +86,7 @@ class SelMeta:
     cu_seqlens_q: torch.Tensor   # int32 [Nseq+1]
     cu_seqlens_k: torch.Tensor   # int32 [Nseq+1]
     tile_off: torch.Tensor       # int32 [4, Nseq+1]
-    meta: torch.Tensor           # int32 [8]
+    meta: torch.Tensor           # int32 [16]: counts, then scratch of the attention kernels
     gate_sum: torch.Tensor       # fp32 [1]
     status: torch.Tensor         # int32 [1] device status word shared by the kernels using this metadata
     n_tokens: int
@@ -120,7 +120,7 @@ def select_rows(gate_or_mask: torch.Tensor, thres: Optional[torch.Tensor], cu_se
     pos_ids = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
     cu_q = torch.empty(nseq + 1, dtype=torch.int32, device=dev)
     tile_off = torch.empty(4, nseq + 1, dtype=torch.int32, device=dev)
-    meta = torch.empty(8, dtype=torch.int32, device=dev)
+    meta = torch.zeros(16, dtype=torch.int32, device=dev)   # LOGO_META_INTS
     gate_sum = torch.empty(1, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     ws_bytes = lib.logo_select_workspace_bytes(n)

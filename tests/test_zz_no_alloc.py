@@ -16,7 +16,7 @@ def _buffers(n, nseq, dev):
                 pos_ids=torch.full((max(n, 1),), -1, dtype=torch.int32, device=dev),
                 cu_q=torch.full((nseq + 1,), -1, dtype=torch.int32, device=dev),
                 tile_off=torch.full((4, nseq + 1), -1, dtype=torch.int32, device=dev),
-                meta=torch.full((8,), -1, dtype=torch.int32, device=dev),
+                meta=torch.full((16,), -1, dtype=torch.int32, device=dev),
                 gate_sum=torch.full((1,), float("nan"), dtype=torch.float32, device=dev),
                 status=torch.zeros(1, dtype=torch.int32, device=dev))
 
@@ -55,7 +55,7 @@ def test_static_scratch_variant_matches_workspace_variant_twice(cuda_device):
         got = _call(lib, True, gate, thres, cu, cuda_device)
         sq = int(want["meta"][0].item())
         assert 0 < sq < n and int(got["status"].item()) == 0 and int(want["status"].item()) == 0
-        assert torch.equal(got["meta"], want["meta"])
+        assert torch.equal(got["meta"][:8], want["meta"][:8])
         assert torch.equal(got["q_idx"][:sq], want["q_idx"][:sq])
         assert torch.equal(got["pos_ids"][:sq], want["pos_ids"][:sq])
         assert torch.equal(got["cu_q"], want["cu_q"])
