@@ -264,6 +264,11 @@ int logo_profile_read(double* total_ms, int* launches, int n);
  *   mode 2: C = A * B     (A staged in tensor memory, B MN-major)
  *   a, b: bf16 [128][128] row-major; c: fp32 [128][128]
  *   flags bit 0: stage A through thread-written swizzled shared memory instead of TMA.
+ *   flags bits 8-23 (timing mode, n > 0): issue the tile product n extra times first and report
+ *     in status[1..3] the clocks spent issuing, the clocks until completion and that span in ns;
+ *     bit 4: N = 64, bit 3: commit after every product, bit 5: alternate accumulators,
+ *     bit 6: first k-step overwrites, bit 7: one elected region per product,
+ *     bits 24-31: number of identical CTAs to launch (status / c come from CTA 0).
  * ------------------------------------------------------------------------------------------ */
 int logo_umma_selftest(int mode, int flags, const void* a, const void* b, float* c, uint32_t lbo_bytes,
                        uint32_t sbo_bytes, uint32_t kstep_bytes, int32_t* status, logo_stream_t stream);

@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __shared__ uint64_t s_full[2], dp_full, ds_ready, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ int s_items[ITEM_RING];
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
   __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
   const ItemRing ring{s_items, item_full, item_empty};
 
@@ -307,10 +307,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     uint32_t n_items = 0;
 
     for (uint32_t n_ring = 0;; ++n_ring) {
-      const long long w = ring_pop(ring, n_ring, ab);
-      if (w < 0) break;
       DqItem it;
-      dq_decode_item(a, (int)w, total_tiles, it);
+      const long long w = ring_pop(ring, n_ring, it, ab);
+      if (w < 0) break;
       if (it.nrows == 0) {
         ring_release(ring, n_ring);
         continue;
@@ -390,23 +389,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      uint32_t kv_iter = 0, n_items = 0;
-      for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_push(ring, n_ring, a.counter_dq, total_items, ab);
-        if (w < 0) break;
-        DqItem it;
-        dq_decode_item(a, (int)w, total_tiles, it);
-        if (it.nrows == 0) continue;
-        const int xq = it.hq * HEAD_DIM, yq = it.bos_q + it.r_base;
-        mbar_wait(&qdo_free, (n_items & 1u) ^ 1u, ab);
-        mbar_arrive_expect_tx(&qdo_full, 2 * TILE_BYTES);
-        tma_load_2d(sQ, &tm_q, &qdo_full, xq, yq);
-        tma_load_2d(sQ + BLK_BYTES, &tm_q, &qdo_full, xq + 64, yq);
-        tma_load_2d(sDO, &tm_do, &qdo_full, xq, yq);
-        tma_load_2d(sDO + BLK_BYTES, &tm_do, &qdo_full, xq + 64, yq);
-        ++n_items;
+      uint32_t kv_iter = 0, n_items = 0, n_pub = 0;
+      DqItem it, it_ahead;
+      auto next_item = [&](DqItem& dst) -> bool {
+        const long long w = ring_claim(a.counter_dq, total_items, ab);
+        if (w >= 0) dq_decode_item(a, (int)w, total_tiles, dst);
+        ring_publish(ring, n_pub++, w, dst, ab);
+        return w >= 0;
+      };
+      bool have = next_item(it);
+      while (have) {
+        if (it.nrows > 0) {
+          const int xq = it.hq * HEAD_DIM, yq = it.bos_q + it.r_base;
+          mbar_wait(&qdo_free, (n_items & 1u) ^ 1u, ab);
+          mbar_arrive_expect_tx(&qdo_full, 2 * TILE_BYTES);
+          tma_load_2d(sQ, &tm_q, &qdo_full, xq, yq);
+          tma_load_2d(sQ + BLK_BYTES, &tm_q, &qdo_full, xq + 64, yq);
+          tma_load_2d(sDO, &tm_do, &qdo_full, xq, yq);
+          tma_load_2d(sDO + BLK_BYTES, &tm_do, &qdo_full, xq + 64, yq);
+          ++n_items;
+        }
+        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's K/V stream
         const int x = it.kvh * HEAD_DIM;
-        for (int j = it.jb; j < it.je; ++j, ++kv_iter) {
+        for (int j = it.jb; it.nrows > 0 && j < it.je; ++j, ++kv_iter) {
           const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
           const int y = it.bos_k + j * TILE;
           mbar_wait(&k_empty[st], ph ^ 1u, ab);
@@ -418,6 +423,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
           tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
         }
+        it = it_ahead;
+        have = have_ahead;
       }
       if (abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -433,26 +440,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       uint32_t kv_iter = 0, n_items = 0;
 
       auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
-          umma_ss(d_tmem, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc_kk,
-                  kk > 0);
-        }
+        umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
+                                     idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, umma_desc_sw128(b_base + (uint32_t)kk * 2048u, BLK_BYTES, 1024),
-                  idesc_mn, acc || kk > 0);
-        }
+        umma_tile_k128<true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_pop(ring, n_ring, ab);
-        if (w < 0) break;
         DqItem it;
-        dq_decode_item(a, (int)w, total_tiles, it);
+        const long long w = ring_pop(ring, n_ring, it, ab);
+        if (w < 0) break;
         if (it.nrows == 0) {
           ring_release(ring, n_ring);
           continue;
@@ -481,6 +479,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             tc_fence_after();
             issue_kk(TM_S + st_n * 128u, q_base, k_base + st_n * TILE_BYTES);
             umma_commit(&s_full[st_n]);
+          } else {
+            // every product that reads Q / dO has been issued: the next item's tiles may come in
+            // while this item's last dQ product and its epilogue run
+            umma_commit(&qdo_free);
           }
           mbar_wait(&ds_ready, kv_iter & 1u, ab);
           tc_fence_after();
@@ -495,7 +497,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           }
         }
         umma_commit(&acc_done);
-        umma_commit(&qdo_free);
         ring_release(ring, n_ring);
       }
     }
@@ -565,7 +566,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __shared__ __align__(16) float s_lse[2][TILE];
   __shared__ __align__(16) float s_delta[2][TILE];
   __shared__ __align__(16) int s_pos[2][TILE];
-  __shared__ int s_items[ITEM_RING];
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
   __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
   const ItemRing ring{s_items, item_full, item_empty};
 
@@ -612,26 +613,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const float c = a.scale_log2;
     uint32_t idx = 0, n_items = 0;
 
-    // loads lse / delta / pos of query tile `i` of head `hq` into registers (threads < 128)
-    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
-      const int r = i * TILE + tid;
-      if (r < it.nsel) {
-        const size_t sidx = (size_t)hq * a.cap + it.bos_q + r;
-        l = __ldg(a.lse_sel + sidx);
-        d = __ldg(a.delta_sel + sidx);
-        p = bwd_row_position(a, it.bos_q, r);
-      } else {
-        l = 0.f;
-        d = 0.f;
-        p = -1;
-      }
+    // Loads lse / delta / pos of query tile `i` of head `hq` into registers. The loads are issued
+    // unconditionally from a clamped row (no select on a loaded value before it is needed, which
+    // would expose the memory round trip); rows past the end are replaced when the values are used.
+    const int vrow = tid & (TILE - 1);
+    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) -> bool {
+      const int r = i * TILE + vrow;
+      const int rc = min(r, it.nsel - 1);
+      const size_t sidx = (size_t)hq * a.cap + it.bos_q + rc;
+      l = __ldg(a.lse_sel + sidx);
+      d = __ldg(a.delta_sel + sidx);
+      p = bwd_row_position(a, it.bos_q, rc);
+      return r < it.nsel;
     };
 
     for (uint32_t n_ring = 0;; ++n_ring) {
-      const long long w = ring_pop(ring, n_ring, ab);
-      if (w < 0) break;
       DkvItem it;
-      dkv_decode_item(a, (int)w, it);
+      const long long w = ring_pop(ring, n_ring, it, ab);
+      if (w < 0) break;
       const int nq = it.i_end - it.i0;
       const int key_pos = it.kv_start + row;
       const bool key_valid = key_pos < it.len_k;
@@ -653,24 +652,41 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const bool partial_keys = it.kv_start + TILE > it.len_k;
 
       // vectors of the first step
-      if (tid < TILE) {
+      {
         float l, d;
         int p;
-        fetch_vec(it, it.kvh * G, it.i0, l, d, p);
-        s_lse[idx & 1u][tid] = l;
-        s_delta[idx & 1u][tid] = d;
-        s_pos[idx & 1u][tid] = p;
+        const bool ok = fetch_vec(it, it.kvh * G, it.i0, l, d, p);
+        if (tid < TILE) {
+          s_lse[idx & 1u][tid] = ok ? l : 0.f;
+          s_delta[idx & 1u][tid] = ok ? d : 0.f;
+          s_pos[idx & 1u][tid] = ok ? p : -1;
+        }
       }
       named_barrier_sync(3, 256);
 
+      int g_nx = 0, i_nx = 0;   // (head of the group, query tile) of step s + 1, advanced without a division
       for (int s = 0; s < n_steps; ++s, ++idx) {
-        const int g = s / nq, i = it.i0 + s % nq;
+        if (++i_nx == nq) {
+          i_nx = 0;
+          ++g_nx;
+        }
         const uint32_t vb = idx & 1u;
         // prefetch the vectors of the next step
-        float nl = 0.f, nd = 0.f;
-        int np = -1;
+        // the vectors of the next step travel global -> shared asynchronously (the buffer they land
+        // in was last read before barrier 2 of the previous step)
         const bool has_next = (s + 1 < n_steps);
-        if (has_next && tid < TILE) fetch_vec(it, it.kvh * G + (s + 1) / nq, it.i0 + (s + 1) % nq, nl, nd, np);
+        bool next_ok = true;
+        if (has_next && tid < TILE) {
+          const int hq_nx = it.kvh * G + g_nx;
+          const int r = (it.i0 + i_nx) * TILE + tid;
+          const int rc = min(r, it.nsel - 1);
+          next_ok = r < it.nsel;
+          const size_t sidx = (size_t)hq_nx * a.cap + it.bos_q + rc;
+          cp_async_4(&s_lse[vb ^ 1u][tid], a.lse_sel + sidx);
+          cp_async_4(&s_delta[vb ^ 1u][tid], a.delta_sel + sidx);
+          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + it.bos_q + rc);
+          else s_pos[vb ^ 1u][tid] = next_ok ? r : -1;
+        }
 
         const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
@@ -706,9 +722,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], pk + 16);
           }
           if (has_next && tid < TILE) {
-            s_lse[vb ^ 1u][tid] = nl;
-            s_delta[vb ^ 1u][tid] = nd;
-            s_pos[vb ^ 1u][tid] = np;
+            cp_async_wait_all();
+            if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
           }
           named_barrier_sync(2, 256);   // all reads of dP^T done; next step's vectors visible
           tmem_st32(TM_DPT + lane_off + (uint32_t)(half * 32), pk);
@@ -755,24 +770,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      uint32_t q_iter = 0, n_items = 0;
-      for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_push(ring, n_ring, a.counter_dkv, total_items, ab);
-        if (w < 0) break;
-        DkvItem it;
-        dkv_decode_item(a, (int)w, it);
-        const int nq = it.i_end - it.i0;
-        if (nq <= 0) continue;
-        const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
-        mbar_wait(&kv_free, (n_items & 1u) ^ 1u, ab);
-        mbar_arrive_expect_tx(&kv_full, 2 * TILE_BYTES);
-        tma_load_2d(sK, &tm_k, &kv_full, xk, yk);
-        tma_load_2d(sK + BLK_BYTES, &tm_k, &kv_full, xk + 64, yk);
-        tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
-        tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
-        ++n_items;
-        for (int s = 0; s < nq * G; ++s, ++q_iter) {
-          const int g = s / nq, i = it.i0 + s % nq;   // query head of the group, query tile
+      uint32_t q_iter = 0, n_items = 0, n_pub = 0;
+      DkvItem it, it_ahead;
+      auto next_item = [&](DkvItem& dst) -> bool {
+        const long long w = ring_claim(a.counter_dkv, total_items, ab);
+        if (w >= 0) dkv_decode_item(a, (int)w, dst);
+        ring_publish(ring, n_pub++, w, dst, ab);
+        return w >= 0;
+      };
+      bool have = next_item(it);
+      while (have) {
+        const int nq = max(it.i_end - it.i0, 0);
+        if (nq > 0) {
+          const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
+          mbar_wait(&kv_free, (n_items & 1u) ^ 1u, ab);
+          mbar_arrive_expect_tx(&kv_full, 2 * TILE_BYTES);
+          tma_load_2d(sK, &tm_k, &kv_full, xk, yk);
+          tma_load_2d(sK + BLK_BYTES, &tm_k, &kv_full, xk + 64, yk);
+          tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
+          tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
+          ++n_items;
+        }
+        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's Q/dO stream
+        int g = 0, i = it.i0;   // query head of the group, query tile
+        for (int s = 0; s < nq * G; ++s, ++q_iter, ++i) {
+          if (i == it.i_end) {
+            i = it.i0;
+            ++g;
+          }
           const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
           const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
           mbar_wait(&q_empty[st], ph ^ 1u, ab);
@@ -784,6 +809,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
           tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
         }
+        it = it_ahead;
+        have = have_ahead;
       }
       if (abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -799,26 +826,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       uint32_t q_iter = 0, n_items = 0;
 
       auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
-          umma_ss(d_tmem, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc_kk,
-                  kk > 0);
-        }
+        umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
+                                     idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          umma_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, umma_desc_sw128(b_base + (uint32_t)kk * 2048u, BLK_BYTES, 1024),
-                  idesc_mn, acc || kk > 0);
-        }
+        umma_tile_k128<true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_pop(ring, n_ring, ab);
-        if (w < 0) break;
         DkvItem it;
-        dkv_decode_item(a, (int)w, it);
+        const long long w = ring_pop(ring, n_ring, it, ab);
+        if (w < 0) break;
         const int nq = it.i_end - it.i0;
         if (nq <= 0) {
           ring_release(ring, n_ring);
@@ -843,6 +861,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           const uint32_t st = q_iter & 1u;
           const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
           const bool has_next = (s + 1 < n_steps);
+          // every product that reads K / V has been issued: the next item's tiles may come in while
+          // this item's last two accumulations and its epilogue run
+          if (!has_next) umma_commit(&kv_free);
           mbar_wait(&p_ready, q_iter & 1u, ab);
           tc_fence_after();
           issue_ts(TM_DV, TM_ST, do_base + st * TILE_BYTES, s > 0);
@@ -865,7 +886,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           }
         }
         umma_commit(&acc_done);
-        umma_commit(&kv_free);
         ring_release(ring, n_ring);
       }
     }

@@ -61,13 +61,16 @@ __device__ __forceinline__ int find_sequence(const int32_t* __restrict__ off, in
 // dynamically from a global counter, so CTAs that drew light items simply take more of them (a
 // static round-robin leaves 10-60 % of the SMs idle at the tail; sorting all items by cost instead
 // balances as well but scatters concurrent CTAs over the K/V streams and costs more in L2 misses
-// than it gains). One thread of the producer warp claims items and publishes them through a small
-// shared-memory ring; the MMA warp and the eight element-wise warps consume them in order.
+// than it gains). One thread of the producer warp claims an item, DECODES it (sequence lookup,
+// binary searches over positions: chains of dependent global loads, microseconds long) and
+// publishes the decoded record through a small shared-memory ring; it does so one item ahead of
+// the loads it issues, so the MMA warp and the eight element-wise warps never wait for a decode.
 constexpr int ITEM_RING = 4;
+constexpr int ITEM_WORDS = 20;          // ints per published record; word 0 is the item index or -1
 constexpr int ITEM_CONSUMER_WARPS = 9;
 
 struct ItemRing {
-  volatile int* items;   // [ITEM_RING]
+  volatile int* items;   // [ITEM_RING][ITEM_WORDS]
   uint64_t* full;        // [ITEM_RING] count 1
   uint64_t* empty;       // [ITEM_RING] count ITEM_CONSUMER_WARPS
 };
@@ -79,27 +82,45 @@ __device__ __forceinline__ void ring_init(const ItemRing& r) {
   }
 }
 
-// Producer (one thread): claim item number `n` of this CTA. Returns the item, or -1 when the list
-// is exhausted; the -1 is published as well so that the consumers stop.
-__device__ __forceinline__ long long ring_push(const ItemRing& r, uint32_t n, int* counter, long long total,
-                                               const AbortState& ab) {
+// Producer (one thread): next unclaimed item, or -1 when the list is exhausted / the CTA aborted.
+__device__ __forceinline__ long long ring_claim(int* counter, long long total, const AbortState& ab) {
+  const long long w = (long long)atomicAdd(counter, 1);
+  return (w >= total || *ab.smem_abort) ? -1 : w;
+}
+
+// Producer (one thread): publish record number `n` of this CTA (w < 0: the end marker).
+template <class Item>
+__device__ __forceinline__ void ring_publish(const ItemRing& r, uint32_t n, long long w, const Item& item,
+                                             const AbortState& ab) {
+  static_assert(sizeof(Item) <= (ITEM_WORDS - 1) * sizeof(int), "item record too large for the ring");
   const uint32_t slot = n % ITEM_RING, ph = (n / ITEM_RING) & 1u;
   mbar_wait(&r.empty[slot], ph ^ 1u, ab);
-  long long w = (long long)atomicAdd(counter, 1);
-  if (w >= total || *ab.smem_abort) w = -1;
-  r.items[slot] = (int)w;
+  volatile int* dst = r.items + slot * ITEM_WORDS;
+  dst[0] = (int)w;
+  if (w >= 0) {
+    const int* src = reinterpret_cast<const int*>(&item);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(Item) / sizeof(int)); ++i) dst[1 + i] = src[i];
+  }
   mbar_arrive(&r.full[slot]);
-  return w;
 }
 
-// Consumer (every thread of the role): the n-th item of this CTA, or -1.
-__device__ __forceinline__ long long ring_pop(const ItemRing& r, uint32_t n, const AbortState& ab) {
+// Consumer (every thread of the role): record number `n` of this CTA; returns the item index or -1.
+template <class Item>
+__device__ __forceinline__ long long ring_pop(const ItemRing& r, uint32_t n, Item& item, const AbortState& ab) {
   const uint32_t slot = n % ITEM_RING, ph = (n / ITEM_RING) & 1u;
   if (!mbar_wait(&r.full[slot], ph, ab)) return -1;
-  return (long long)r.items[slot];
+  const volatile int* src = r.items + slot * ITEM_WORDS;
+  const int w = src[0];
+  if (w >= 0) {
+    int* dst = reinterpret_cast<int*>(&item);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(Item) / sizeof(int)); ++i) dst[i] = src[1 + i];
+  }
+  return (long long)w;
 }
 
-// Consumer: the calling WARP is done with item `n` (call from all lanes; one arrives).
+// Consumer: the calling WARP is done with record `n` (call from all lanes; one arrives).
 __device__ __forceinline__ void ring_release(const ItemRing& r, uint32_t n) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(&r.empty[n % ITEM_RING]);

@@ -87,15 +87,16 @@ __device__ __forceinline__ void mask_chunk(uint32_t (&r)[32], int k0, int key_hi
 }
 
 __device__ __forceinline__ float max_chunk(const uint32_t (&r)[32]) {
-  float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
+  float m[4];
 #pragma unroll
-  for (int i = 4; i < 32; i += 4) {
-    m0 = fmaxf(m0, __uint_as_float(r[i]));
-    m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-    m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
-    m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+  for (int c4 = 0; c4 < 4; ++c4) {
+    const uint32_t* v = r + 8 * c4;
+    float x = fmax3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+    x = fmax3(x, __uint_as_float(v[3]), __uint_as_float(v[4]));
+    x = fmax3(x, __uint_as_float(v[5]), __uint_as_float(v[6]));
+    m[c4] = fmaxf(x, __uint_as_float(v[7]));
   }
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  return fmaxf(fmax3(m[0], m[1], m[2]), m[3]);
 }
 
 // p = 2^(s*c - mc) for 32 scores, packed to 16 bf16x2 words; the fp32 values are summed into l0 / l1
@@ -111,6 +112,39 @@ __device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], float c,
   }
 }
 
+// One softmax group (128 threads, `row` = thread index inside it) copies the query rows of its
+// tile into 128-byte swizzled shared memory. All sixteen index loads, then all sixteen row loads,
+// are issued back to back (no branch between them), so the copy costs two memory round trips.
+__device__ __forceinline__ void gather_query_tile(const AttnArgs& a, const FwdItem& it, int t, int row, uint8_t* sQt) {
+  const int nrows = it.nrows[t];
+  const int r_base = it.row0 + t * TILE;
+  const int ch = row & 15;  // 16-byte chunk of the 256-byte row
+  uint32_t tok[16];   // token indices fit 31 bits (n_tokens is an int)
+  uint32_t ok_mask = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int r = i * 8 + (row >> 4);
+    const long long tk = row_token(a, it.bos_q, it.bos_k, r_base + min(r, nrows - 1));
+    const bool ok = tk >= 0 && tk < a.n_tokens;
+    ok_mask |= (uint32_t)ok << i;
+    tok[i] = ok ? (uint32_t)tk : 0u;
+  }
+  uint4 vals[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    vals[i] = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)tok[i] * a.hq + it.hq) * HEAD_DIM) + ch);
+  if (ok_mask != 0xffffu && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int r = i * 8 + (row >> 4);
+    const bool keep = (r < nrows) && ((ok_mask >> i) & 1u);
+    uint4 v = vals[i];
+    if (!keep) v = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(sQt + (ch >> 3) * BLK_BYTES + sw128_offset((uint32_t)r, (uint32_t)(ch & 7) * 8)) = v;
+  }
+  fence_proxy_async_smem();
+}
+
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const AttnArgs a) {
@@ -124,7 +158,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   __shared__ uint64_t q_ready[2], s_full[2], p_ready[2], o_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ int s_items[ITEM_RING];
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
   __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
   const ItemRing ring{s_items, item_full, item_empty};
 
@@ -176,47 +210,39 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     uint32_t n_steps = 0;   // (tile, key-step) pairs processed so far == S / P / O barrier phases
     uint32_t n_items = 0;   // items in which this tile was active
 
-    for (uint32_t n_ring = 0;; ++n_ring) {
-      const long long w = ring_pop(ring, n_ring, ab);
-      if (w < 0) break;
-      FwdItem it;
-      fwd_decode_item(a, (int)w, total_pairs, it);
+    // Items are walked one ahead: as soon as the last score tile of an item has been read, the
+    // rows of the NEXT item are copied into shared memory (Q is free by then), so the tensor pipe
+    // computes its first scores while this group still writes the current item's output.
+    uint32_t n_ring = 0;
+    FwdItem it;
+    long long w = ring_pop(ring, n_ring, it, ab);
+    if (w >= 0) {
+      if (it.nrows[t] > 0) {
+        gather_query_tile(a, it, t, row, sQt);
+        tc_fence_before();
+        mbar_arrive(&q_ready[t]);
+      }
+    }
+    while (w >= 0) {
       const int nrows = it.nrows[t];
+      FwdItem it_next;
+      long long w_next;
       if (nrows == 0) {
+        w_next = ring_pop(ring, n_ring + 1, it_next, ab);
+        if (w_next >= 0) {
+          if (it_next.nrows[t] > 0) {
+            gather_query_tile(a, it_next, t, row, sQt);
+            tc_fence_before();
+            mbar_arrive(&q_ready[t]);
+          }
+        }
         ring_release(ring, n_ring);
+        it = it_next;
+        w = w_next;
+        ++n_ring;
         continue;
       }
       const int r_base = it.row0 + t * TILE;
-
-      // ---- gather the query rows into swizzled shared memory ----
-      {
-        const int ch = row & 15;  // 16-byte chunk of the 256-byte row
-        uint4 vals[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int r = i * 8 + (row >> 4);
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (r < nrows) {
-            const long long tok = row_token(a, it.bos_q, it.bos_k, r_base + r);
-            if (tok >= 0 && tok < a.n_tokens) {
-              v = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.hq + it.hq) * HEAD_DIM) + ch);
-            } else if (a.status) {
-              atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
-            }
-          }
-          vals[i] = v;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int r = i * 8 + (row >> 4);
-          *reinterpret_cast<uint4*>(sQt + (ch >> 3) * BLK_BYTES + sw128_offset((uint32_t)r, (uint32_t)(ch & 7) * 8)) =
-              vals[i];
-        }
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&q_ready[t]);
-      ++n_items;
 
       const int my_r = min(row, nrows - 1);
       const int my_pos = row_position(a, it.bos_q, r_base + my_r);
@@ -299,13 +325,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
 
       // ---- epilogue: O / l -> bf16 rows of the output, log-sum-exp ----
-      mbar_wait(&o_done[t], (n_steps - 1u) & 1u, ab);
-      tc_fence_after();
       const bool row_valid = row < nrows;
       const long long tok = row_valid ? row_token(a, it.bos_q, it.bos_k, r_base + row) : -1;
       const bool store = row_valid && tok >= 0 && tok < a.n_tokens;
       const float inv_l = 1.f / l_run;
       __nv_bfloat16* orow = a.o + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM;
+      float* lse_out = (store && a.lse) ? a.lse + (size_t)tok * a.hq + it.hq : nullptr;
+
+      w_next = ring_pop(ring, n_ring + 1, it_next, ab);
+      if (w_next >= 0) {
+        if (it_next.nrows[t] > 0) {
+          gather_query_tile(a, it_next, t, row, sQt);
+          tc_fence_before();
+          mbar_arrive(&q_ready[t]);
+        }
+      }
+
+      mbar_wait(&o_done[t], (n_steps - 1u) & 1u, ab);
+      tc_fence_after();
 #pragma unroll 1
       for (int chk = 0; chk < 4; ++chk) {
         uint32_t r[32];
@@ -324,9 +361,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
         }
       }
-      if (store && a.lse) a.lse[(size_t)tok * a.hq + it.hq] = m_run * c + log2f(l_run);
+      if (lse_out) *lse_out = m_run * c + log2f(l_run);
       tc_fence_before();
       ring_release(ring, n_ring);
+      it = it_next;
+      w = w_next;
+      ++n_ring;
     }
   } else if (warp == 8) {
     // =====================================================================================
@@ -335,12 +375,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      uint32_t kv_iter = 0;
-      for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_push(ring, n_ring, a.work_counter, total_items, ab);
-        if (w < 0) break;
-        FwdItem it;
-        fwd_decode_item(a, (int)w, total_pairs, it);
+      uint32_t kv_iter = 0, n_pub = 0;
+      FwdItem it, it_ahead;
+      // claim + decode + publish one record; false once the list is exhausted (end marker published)
+      auto next_item = [&](FwdItem& dst) -> bool {
+        const long long w = ring_claim(a.work_counter, total_items, ab);
+        if (w >= 0) fwd_decode_item(a, (int)w, total_pairs, dst);
+        ring_publish(ring, n_pub++, w, dst, ab);
+        return w >= 0;
+      };
+      bool have = next_item(it);
+      while (have) {
+        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's loads
         const int x = it.kvh * HEAD_DIM;
         for (int j = it.JB; j < it.JE; ++j, ++kv_iter) {
           const uint32_t st = kv_iter % FWD_STAGES;
@@ -355,6 +401,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
           tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
         }
+        it = it_ahead;
+        have = have_ahead;
       }
       // On an aborted run copies may still be in flight: give them a bounded time to land
       // before the CTA's shared memory is released.
@@ -377,30 +425,20 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       uint32_t n_items[2] = {0, 0};  // items per tile
 
       auto issue_s = [&](int t, uint32_t st) {
-        const uint32_t qb = q_base + (uint32_t)t * TILE_BYTES, kb = k_base + st * TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK_BYTES + (uint32_t)(kk & 3) * 32u;
-          umma_ss(tmem + (uint32_t)t * 128u, umma_desc_sw128(qb + off, 0, 1024), umma_desc_sw128(kb + off, 0, 1024),
-                  idesc_qk, kk > 0);
-        }
+        umma_tile_k128<false, false>(tmem + (uint32_t)t * 128u, umma_desc_sw128(q_base + (uint32_t)t * TILE_BYTES, 0, 1024),
+                                     umma_desc_sw128(k_base + st * TILE_BYTES, 0, 1024), idesc_qk, 0u);
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, uint32_t st, bool acc) {
-        const uint32_t vb = v_base + st * TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          umma_ts(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)kk * 8u,
-                  umma_desc_sw128(vb + (uint32_t)kk * 2048u, BLK_BYTES, 1024), idesc_pv, acc || kk > 0);
-        }
+        umma_tile_k128<true, true>(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u,
+                                   umma_desc_sw128(v_base + st * TILE_BYTES, BLK_BYTES, 1024), idesc_pv, acc ? 1u : 0u);
         umma_commit(&o_done[t]);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
-        const long long w = ring_pop(ring, n_ring, ab);
-        if (w < 0) break;
         FwdItem it;
-        fwd_decode_item(a, (int)w, total_pairs, it);
+        const long long w = ring_pop(ring, n_ring, it, ab);
+        if (w < 0) break;
         if (it.JE <= it.JB) {
           ring_release(ring, n_ring);
           continue;

@@ -93,14 +93,18 @@ struct AbortState {
 // after a number of failed (each up to LOGO_TRYWAIT_HINT_NS long) attempts.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortState& ab) {
   if (mbar_try_wait(bar, parity)) return true;
-  if (*ab.smem_abort) return false;
-  const uint64_t t0 = globaltimer_ns();
+  // failed attempts between two looks at the clock: few when each attempt sleeps, many when it polls
+  constexpr uint32_t kCheckMask = (LOGO_TRYWAIT_HINT_NS >= 100000u) ? 15u : 8191u;
+  uint64_t t0 = 0;
 #pragma unroll 1
-  for (uint32_t it = 0;; ++it) {
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 15u) == 15u) {
+    if ((it & kCheckMask) == 0u) {
       if (*ab.smem_abort) return false;
-      if (globaltimer_ns() - t0 > LOGO_WAIT_TIMEOUT_NS) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > LOGO_WAIT_TIMEOUT_NS) {
         *ab.smem_abort = 1;
         if (ab.gmem_status) atomicCAS(ab.gmem_status, 0, (int)DEV_WAIT_TIMEOUT);
         return false;
@@ -240,6 +244,48 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
   __syncwarp();
 }
 
+// A whole 128 x N x 128 tile product (eight k-steps of 16) issued inside ONE elected region: the
+// operand descriptors advance by constants (the start-address field counts 16-byte units and cannot
+// carry out of its 14 bits for addresses inside the 228 KB of shared memory), so the issuing lane
+// spends a handful of uniform-register adds per instruction instead of rebuilding descriptors.
+//   A_TMEM: A comes from tensor memory (8 columns per k-step), else from K-major 128B-swizzled
+//           shared memory (two [128][64] blocks: 32 bytes per k-step, 16 KB between the blocks);
+//   B_MN  : B is MN-major ([k][n] rows as they lie in memory, 2 KB per k-step), else K-major.
+template <bool A_TMEM, bool B_MN>
+__device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
+                                               uint32_t accumulate_first) {
+  if (elect_one()) {
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint32_t kmaj = (uint32_t)(kk >> 2) * 1024u + (uint32_t)(kk & 3) * 2u;   // K-major advance, 16 B units
+      const uint64_t b = b0 + (B_MN ? (uint64_t)kk * 128u : (uint64_t)kmaj);
+      const uint32_t acc = kk > 0 ? 1u : accumulate_first;
+      if (A_TMEM) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+            "}\n"
+            :
+            : "r"(d_tmem), "r"((uint32_t)a0 + (uint32_t)kk * 8u), "l"(b), "r"(idesc), "r"(acc)
+            : "memory");
+      } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}\n"
+            :
+            : "r"(d_tmem), "l"(a0 + (uint64_t)kmaj), "l"(b), "r"(idesc), "r"(acc)
+            : "memory");
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // Make `bar` track completion of all tcgen05 async ops issued so far by the elected lane.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   if (elect_one()) {
@@ -301,6 +347,22 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint
 // ---------------------------------------------------------------------------
 // small math helpers
 // ---------------------------------------------------------------------------
+// 4-byte asynchronous copy global -> shared (no destination register, hence no scoreboard wait
+// anywhere near the issue point); completion with cp_async_wait_all().
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// max of three floats in one instruction (3-input max.f32, sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

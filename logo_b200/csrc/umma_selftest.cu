@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(128, 1)
   uint8_t* sB = smem + 32768;
   __shared__ uint64_t bar_load;
   __shared__ uint64_t bar_mma;
+  __shared__ uint64_t bar_scratch;   // timing mode, bit 3: receives a commit after every tile product
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -39,6 +40,7 @@ __global__ void __launch_bounds__(128, 1)
     abort_flag = 0;
     mbar_init(&bar_load, 1);
     mbar_init(&bar_mma, 1);
+    mbar_init(&bar_scratch, 1u << 20);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -105,17 +107,38 @@ __global__ void __launch_bounds__(128, 1)
     mbar_wait(&bar_load, 0, ab);
     const uint32_t a_base = smem_u32(sA);
     const uint32_t b_base = smem_u32(sB);
-    const int repeat = (args.flags >> 8) & 0xffff;   // timing mode: issue the tile product `repeat` extra times
+    const int repeat = (args.flags >> 8) & 0xffff;   // bits 8-23   // timing mode: issue the tile product `repeat` extra times
     const int n_cols = ((args.flags >> 4) & 1) ? 64 : 128;
     if (repeat > 0) {
+      // timing-mode options: bit 5 alternates between two accumulators from one tile product to the
+      // next (mode 0 only: the second one overlaps the staged A operand of mode 2), bit 6 makes the
+      // first k-step of every tile product overwrite instead of accumulate
+      const bool alt_acc = (args.flags >> 5) & 1, overwrite = (args.flags >> 6) & 1;
+      const bool batched = (args.flags >> 7) & 1;   // bit 7: one elected region per tile product
+      const bool commit_each = (args.flags >> 3) & 1;
+      const uint64_t g0 = globaltimer_ns();
       const long long t0 = clock64();
       for (int rep = 0; rep < repeat; ++rep) {
-        if (args.mode == 0) {
+        if (batched) {
+          if (args.mode == 0)
+            umma_tile_k128<false, false>(tmem_d, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
+                                         umma_idesc_bf16(128, n_cols, 0, 0), overwrite ? 0 : 1);
+          else if (args.mode == 1)
+            umma_tile_k128<false, true>(tmem_d, umma_desc_sw128(a_base, 0, 1024),
+                                        umma_desc_sw128(b_base, args.lbo, args.sbo), umma_idesc_bf16(128, n_cols, 0, 1),
+                                        overwrite ? 0 : 1);
+          else
+            umma_tile_k128<true, true>(tmem_d, tmem_p, umma_desc_sw128(b_base, args.lbo, args.sbo),
+                                       umma_idesc_bf16(128, n_cols, 0, 1), overwrite ? 0 : 1);
+          if (commit_each) umma_commit(&bar_scratch);
+        } else if (args.mode == 0) {
           const uint32_t idesc = umma_idesc_bf16(128, n_cols, 0, 0);
+          const uint32_t d = tmem_d + ((alt_acc && (rep & 1)) ? 128u : 0u);
 #pragma unroll 1
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
-            umma_ss(tmem_d, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc, 1);
+            umma_ss(d, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), idesc,
+                    (overwrite && kk == 0) ? 0 : 1);
           }
         } else if (args.mode == 1) {
           const uint32_t idesc = umma_idesc_bf16(128, n_cols, 0, 1);
@@ -138,9 +161,11 @@ __global__ void __launch_bounds__(128, 1)
       umma_commit(&bar_mma);
       mbar_wait(&bar_mma, 0, ab);
       const long long t2 = clock64();
-      if (tid == 0 && status) {
+      const uint64_t g1 = globaltimer_ns();
+      if (tid == 0 && status && blockIdx.x == 0) {
         status[1] = (int)(t1 - t0);   // clocks spent issuing
         status[2] = (int)(t2 - t0);   // clocks until the last product completed
+        status[3] = (int)(g1 - g0);   // the same span in nanoseconds (gives the SM clock under this load)
       }
       __syncwarp();
       if (tid == 0) {
@@ -187,8 +212,10 @@ __global__ void __launch_bounds__(128, 1)
       uint32_t r[32];
       tmem_ld32(tmem_addr(tmem_d, lane_base, ch * 32), r);
       tmem_ld_wait();
+      if (blockIdx.x == 0) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) c[(size_t)tid * 128 + ch * 32 + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) c[(size_t)tid * 128 + ch * 32 + i] = __uint_as_float(r[i]);
+      }
     }
   }
   tc_fence_before();
@@ -211,7 +238,8 @@ extern "C" int logo_umma_selftest(int mode, int flags, const void* a, const void
   const int smem_bytes = 65536 + 1024;
   LOGO_CHECK_CUDA(cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   SelftestArgs args{mode, flags, lbo_bytes, sbo_bytes, kstep_bytes};
-  umma_selftest_kernel<<<1, 128, smem_bytes, (cudaStream_t)stream>>>(tm_a, tm_b, (const __nv_bfloat16*)a, c, status,
+  const int grid = ((flags >> 24) & 0xff) ? ((flags >> 24) & 0xff) : 1;   // timing mode: identical CTAs load the chip
+  umma_selftest_kernel<<<grid, 128, smem_bytes, (cudaStream_t)stream>>>(tm_a, tm_b, (const __nv_bfloat16*)a, c, status,
                                                                      args);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
