@@ -258,6 +258,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
   __shared__ uint64_t qdo_full, qdo_free, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ uint64_t s_full[2], dp_full, ds_ready, acc_done;
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_items[ITEM_RING * ITEM_WORDS];
@@ -361,24 +362,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       if (row < it.nrows)
         tok = a.q_idx ? __ldg(a.q_idx + it.bos_q + it.r_base + row) : (long long)(it.bos_k + it.r_base + row);
       const bool store = tok >= 0 && tok < a.n_tokens;
-      __nv_bfloat16* dst_row = a.dq + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM + col0;
+      const long long row_off = store ? (long long)(((size_t)tok * a.hq + it.hq) * HEAD_DIM + col0) : -1;
 #pragma unroll
       for (int chk = 0; chk < 2; ++chk) {
-        uint32_t r[32];
+        uint32_t r[32], pk[16];
         tmem_ld32(TM_DQ + lane_off + (uint32_t)col0 + chk * 32, r);
         tmem_ld_wait();
-        if (store) {
-          uint4* dst = reinterpret_cast<uint4*>(dst_row + chk * 32);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * a.scale, __uint_as_float(r[8 * g + 1]) * a.scale);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * a.scale, __uint_as_float(r[8 * g + 3]) * a.scale);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * a.scale, __uint_as_float(r[8 * g + 5]) * a.scale);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * a.scale, __uint_as_float(r[8 * g + 7]) * a.scale);
-            dst[g] = v;
-          }
-        }
+        for (int i = 0; i < 16; ++i)
+          pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * a.scale, __uint_as_float(r[2 * i + 1]) * a.scale);
+        store_patch_32x32(s_stage[warp], pk, a.dq, row_off >= 0 ? row_off + chk * 32 : -1, lane);
       }
       tc_fence_before();
       ring_release(ring, n_ring);
@@ -391,10 +384,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_v);
       uint32_t kv_iter = 0, n_items = 0, n_pub = 0;
       DqItem it, it_ahead;
+      long long w_last = -1;
       auto next_item = [&](DqItem& dst) -> bool {
         const long long w = ring_claim(a.counter_dq, total_items, ab);
         if (w >= 0) dq_decode_item(a, (int)w, total_tiles, dst);
         ring_publish(ring, n_pub++, w, dst, ab);
+        w_last = w;
         return w >= 0;
       };
       bool have = next_item(it);
@@ -409,7 +404,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sDO + BLK_BYTES, &tm_do, &qdo_full, xq + 64, yq);
           ++n_items;
         }
-        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's K/V stream
+        // Look one item ahead (decode and publish it before this item's K/V stream) while the list is long;
+        // near its end claim late, so that no CTA sits on an item another CTA could already run.
+        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
+        bool have_ahead = ahead ? next_item(it_ahead) : false;
         const int x = it.kvh * HEAD_DIM;
         for (int j = it.jb; it.nrows > 0 && j < it.je; ++j, ++kv_iter) {
           const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
@@ -423,6 +421,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
           tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
         }
+        if (!ahead) have_ahead = next_item(it_ahead);
         it = it_ahead;
         have = have_ahead;
       }
@@ -566,6 +565,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   __shared__ __align__(16) float s_lse[2][TILE];
   __shared__ __align__(16) float s_delta[2][TILE];
   __shared__ __align__(16) int s_pos[2][TILE];
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
   __shared__ int s_items[ITEM_RING * ITEM_WORDS];
   __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
   const ItemRing ring{s_items, item_full, item_empty};
@@ -627,10 +627,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       return r < it.nsel;
     };
 
-    for (uint32_t n_ring = 0;; ++n_ring) {
-      DkvItem it;
-      const long long w = ring_pop(ring, n_ring, it, ab);
-      if (w < 0) break;
+    // Items are walked one ahead: during the last step of an item the next record is popped and its
+    // first-step vectors start travelling to shared memory, so the next item begins without a
+    // memory round trip.
+    uint32_t n_ring = 0;
+    DkvItem it;
+    long long w = ring_pop(ring, n_ring, it, ab);
+    bool vec_ready = false;   // the first-step vectors of `it` are already in s_*[idx & 1]
+    while (w >= 0) {
+      DkvItem it_next;
+      long long w_next = -1;
+      bool vec_next = false;
       const int nq = it.i_end - it.i0;
       const int key_pos = it.kv_start + row;
       const bool key_valid = key_pos < it.len_k;
@@ -645,14 +652,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             reinterpret_cast<uint4*>(dv_row)[g] = make_uint4(0, 0, 0, 0);
           }
         }
+        w_next = ring_pop(ring, n_ring + 1, it_next, ab);
         ring_release(ring, n_ring);
+        it = it_next;
+        w = w_next;
+        vec_ready = false;
+        ++n_ring;
         continue;
       }
       const int n_steps = nq * G;
       const bool partial_keys = it.kv_start + TILE > it.len_k;
 
-      // vectors of the first step
-      {
+      // vectors of the first step, unless the previous item already fetched them
+      if (!vec_ready) {
         float l, d;
         int p;
         const bool ok = fetch_vec(it, it.kvh * G, it.i0, l, d, p);
@@ -661,8 +673,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           s_delta[idx & 1u][tid] = ok ? d : 0.f;
           s_pos[idx & 1u][tid] = ok ? p : -1;
         }
+        named_barrier_sync(3, 256);
       }
-      named_barrier_sync(3, 256);
 
       int g_nx = 0, i_nx = 0;   // (head of the group, query tile) of step s + 1, advanced without a division
       for (int s = 0; s < n_steps; ++s, ++idx) {
@@ -676,15 +688,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         // in was last read before barrier 2 of the previous step)
         const bool has_next = (s + 1 < n_steps);
         bool next_ok = true;
-        if (has_next && tid < TILE) {
-          const int hq_nx = it.kvh * G + g_nx;
-          const int r = (it.i0 + i_nx) * TILE + tid;
-          const int rc = min(r, it.nsel - 1);
-          next_ok = r < it.nsel;
-          const size_t sidx = (size_t)hq_nx * a.cap + it.bos_q + rc;
+        if (!has_next) {
+          w_next = ring_pop(ring, n_ring + 1, it_next, ab);
+          vec_next = (w_next >= 0) && (it_next.i_end > it_next.i0);
+        }
+        if ((has_next || vec_next) && tid < TILE) {
+          const DkvItem& src = has_next ? it : it_next;
+          const int hq_nx = src.kvh * G + (has_next ? g_nx : 0);
+          const int r = (src.i0 + (has_next ? i_nx : 0)) * TILE + tid;
+          const int rc = min(r, src.nsel - 1);
+          next_ok = r < src.nsel;
+          const size_t sidx = (size_t)hq_nx * a.cap + src.bos_q + rc;
           cp_async_4(&s_lse[vb ^ 1u][tid], a.lse_sel + sidx);
           cp_async_4(&s_delta[vb ^ 1u][tid], a.delta_sel + sidx);
-          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + it.bos_q + rc);
+          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + src.bos_q + rc);
           else s_pos[vb ^ 1u][tid] = next_ok ? r : -1;
         }
 
@@ -721,7 +738,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], pk);
             ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], pk + 16);
           }
-          if (has_next && tid < TILE) {
+          if ((has_next || vec_next) && tid < TILE) {
             cp_async_wait_all();
             if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
           }
@@ -737,32 +754,31 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       mbar_wait(&acc_done, n_items & 1u, ab);
       tc_fence_after();
       ++n_items;
+      {
+        const long long row_off =
+            key_valid ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0) : -1;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
-        const float mul = (which == 0) ? a.scale : 1.f;
-        __nv_bfloat16* dst_row = (which == 0) ? dk_row : dv_row;
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
+          const float mul = (which == 0) ? a.scale : 1.f;
 #pragma unroll
-        for (int chk = 0; chk < 2; ++chk) {
-          uint32_t r[32];
-          tmem_ld32(base + chk * 32, r);
-          tmem_ld_wait();
-          if (key_valid) {
-            uint4* dst = reinterpret_cast<uint4*>(dst_row + chk * 32);
+          for (int chk = 0; chk < 2; ++chk) {
+            uint32_t r[32], pk[16];
+            tmem_ld32(base + chk * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-            for (int gg = 0; gg < 4; ++gg) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * gg + 0]) * mul, __uint_as_float(r[8 * gg + 1]) * mul);
-              v.y = pack_bf16x2(__uint_as_float(r[8 * gg + 2]) * mul, __uint_as_float(r[8 * gg + 3]) * mul);
-              v.z = pack_bf16x2(__uint_as_float(r[8 * gg + 4]) * mul, __uint_as_float(r[8 * gg + 5]) * mul);
-              v.w = pack_bf16x2(__uint_as_float(r[8 * gg + 6]) * mul, __uint_as_float(r[8 * gg + 7]) * mul);
-              dst[gg] = v;
-            }
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
+            store_patch_32x32(s_stage[warp], pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
           }
         }
       }
       tc_fence_before();
       ring_release(ring, n_ring);
+      it = it_next;
+      w = w_next;
+      vec_ready = vec_next;
+      ++n_ring;
     }
   } else if (warp == 8) {
     if (lane == 0) {
@@ -772,10 +788,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_prefetch_desc(&tm_v);
       uint32_t q_iter = 0, n_items = 0, n_pub = 0;
       DkvItem it, it_ahead;
+      long long w_last = -1;
       auto next_item = [&](DkvItem& dst) -> bool {
         const long long w = ring_claim(a.counter_dkv, total_items, ab);
         if (w >= 0) dkv_decode_item(a, (int)w, dst);
         ring_publish(ring, n_pub++, w, dst, ab);
+        w_last = w;
         return w >= 0;
       };
       bool have = next_item(it);
@@ -791,7 +809,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
           ++n_items;
         }
-        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's Q/dO stream
+        // Look one item ahead (decode and publish it before this item's Q/dO stream) while the list is long;
+        // near its end claim late, so that no CTA sits on an item another CTA could already run.
+        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
+        bool have_ahead = ahead ? next_item(it_ahead) : false;
         int g = 0, i = it.i0;   // query head of the group, query tile
         for (int s = 0; s < nq * G; ++s, ++q_iter, ++i) {
           if (i == it.i_end) {
@@ -809,6 +830,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
           tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
         }
+        if (!ahead) have_ahead = next_item(it_ahead);
         it = it_ahead;
         have = have_ahead;
       }

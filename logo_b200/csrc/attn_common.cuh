@@ -126,6 +126,33 @@ __device__ __forceinline__ void ring_release(const ItemRing& r, uint32_t n) {
   if ((threadIdx.x & 31) == 0) mbar_arrive(&r.empty[n % ITEM_RING]);
 }
 
+// Epilogue helper. After a 32x32b tensor-memory load every lane owns one ROW of the tile; storing
+// it directly makes each store instruction touch 32 different lines (the epilogue of one tile then
+// costs thousands of cycles of address processing). This routine sends a [32 rows][32 columns] bf16
+// patch (16 packed words per lane) through a warp-private 2 KB shared-memory buffer and writes it
+// back out with 4 lanes per row: one instruction covers 8 rows x 64 contiguous bytes. Both
+// shared-memory passes are free of bank conflicts (16-byte chunks XOR-swizzled by row / 2).
+//   stage      : 2 KB, 16-byte aligned, private to the calling warp
+//   base       : tensor the rows live in
+//   my_row_off : element offset of (this lane's row, first column of the patch), or -1 to skip the row
+__device__ __forceinline__ void store_patch_32x32(uint8_t* stage, const uint32_t* pk, __nv_bfloat16* base,
+                                                  long long my_row_off, int lane) {
+  uint8_t* wr = stage + lane * 64;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(wr + (((c ^ (lane >> 1)) & 3) << 4)) =
+        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = 8 * k + (lane >> 2), c = lane & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + (((c ^ (r >> 1)) & 3) << 4));
+    const long long off = __shfl_sync(0xffffffffu, my_row_off, r);
+    if (off >= 0) *reinterpret_cast<uint4*>(base + off + c * 8) = v;
+  }
+  __syncwarp();
+}
+
 // Position of compacted row `r` (relative to the start of the sequence's compacted rows).
 __device__ __forceinline__ int row_position(const AttnArgs& a, int bos_q, int r) {
   return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;

@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   __shared__ uint64_t k_full[FWD_STAGES], k_empty[FWD_STAGES], v_full[FWD_STAGES], v_empty[FWD_STAGES];
   __shared__ uint64_t q_ready[2], s_full[2], p_ready[2], o_done[2];
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_items[ITEM_RING * ITEM_WORDS];
@@ -343,23 +344,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
       mbar_wait(&o_done[t], (n_steps - 1u) & 1u, ab);
       tc_fence_after();
+      const long long row_off = store ? (long long)(orow - a.o) : -1;
 #pragma unroll 1
       for (int chk = 0; chk < 4; ++chk) {
-        uint32_t r[32];
+        uint32_t r[32], pk[16];
         tmem_ld32(tO + chk * 32, r);
         tmem_ld_wait();
-        if (store) {
-          uint4* dst = reinterpret_cast<uint4*>(orow + chk * 32);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv_l, __uint_as_float(r[8 * g + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv_l, __uint_as_float(r[8 * g + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv_l, __uint_as_float(r[8 * g + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv_l, __uint_as_float(r[8 * g + 7]) * inv_l);
-            dst[g] = v;
-          }
-        }
+        for (int i = 0; i < 16; ++i)
+          pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+        store_patch_32x32(s_stage[warp], pk, a.o, row_off >= 0 ? row_off + chk * 32 : -1, lane);
       }
       if (lse_out) *lse_out = m_run * c + log2f(l_run);
       tc_fence_before();
@@ -377,16 +371,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       tma_prefetch_desc(&tm_v);
       uint32_t kv_iter = 0, n_pub = 0;
       FwdItem it, it_ahead;
+      long long w_last = -1;
       // claim + decode + publish one record; false once the list is exhausted (end marker published)
       auto next_item = [&](FwdItem& dst) -> bool {
         const long long w = ring_claim(a.work_counter, total_items, ab);
         if (w >= 0) fwd_decode_item(a, (int)w, total_pairs, dst);
         ring_publish(ring, n_pub++, w, dst, ab);
+        w_last = w;
         return w >= 0;
       };
       bool have = next_item(it);
       while (have) {
-        const bool have_ahead = next_item(it_ahead);   // decoded and published before this item's loads
+        // Look one item ahead (decode and publish it before this item's loads) while the list is long;
+        // near its end claim late, so that no CTA sits on an item another CTA could already run.
+        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
+        bool have_ahead = ahead ? next_item(it_ahead) : false;
         const int x = it.kvh * HEAD_DIM;
         for (int j = it.JB; j < it.JE; ++j, ++kv_iter) {
           const uint32_t st = kv_iter % FWD_STAGES;
@@ -401,6 +400,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           tma_load_2d(sV + st * TILE_BYTES, &tm_v, &v_full[st], x, y);
           tma_load_2d(sV + st * TILE_BYTES + BLK_BYTES, &tm_v, &v_full[st], x + 64, y);
         }
+        if (!ahead) have_ahead = next_item(it_ahead);
         it = it_ahead;
         have = have_ahead;
       }
