@@ -457,32 +457,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         mbar_wait(&qdo_full, n_items & 1u, ab);
         ++n_items;
         tc_fence_after();
+        // Issue order. dQ(j) and dP(j+1) go out the moment dS(j) is ready (they are the dependency
+        // chain of the element-wise warps); the scores run two key tiles ahead into the S buffer the
+        // warps finished reading a step earlier, so a K tile that is still in flight delays nothing.
+        const int n_kt = it.je - it.jb;
         {
           const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
           mbar_wait(&k_full[st], ph, ab);
           tc_fence_after();
-          issue_kk(TM_S + (kv_iter & 1u) * 128u, q_base, k_base + st * TILE_BYTES);
-          umma_commit(&s_full[kv_iter & 1u]);
+          issue_kk(TM_S + st * 128u, q_base, k_base + st * TILE_BYTES);
+          umma_commit(&s_full[st]);
           mbar_wait(&v_full[st], ph, ab);
           tc_fence_after();
           issue_kk(TM_DP, do_base, v_base + st * TILE_BYTES);
           umma_commit(&dp_full);
           umma_commit(&v_empty[st]);
-        }
-        for (int j = it.jb; j < it.je; ++j, ++kv_iter) {
-          const uint32_t st = kv_iter & 1u;
-          const uint32_t nx = kv_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
-          const bool has_next = (j + 1 < it.je);
-          if (has_next) {
+          if (n_kt > 1) {
+            const uint32_t nx = kv_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
             mbar_wait(&k_full[st_n], ph_n, ab);
             tc_fence_after();
             issue_kk(TM_S + st_n * 128u, q_base, k_base + st_n * TILE_BYTES);
             umma_commit(&s_full[st_n]);
-          } else {
-            // every product that reads Q / dO has been issued: the next item's tiles may come in
-            // while this item's last dQ product and its epilogue run
-            umma_commit(&qdo_free);
           }
+        }
+        for (int j = it.jb; j < it.je; ++j, ++kv_iter) {
+          const uint32_t st = kv_iter & 1u;
+          const uint32_t nx = kv_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
+          const uint32_t nx2 = kv_iter + 2u, ph_n2 = (nx2 >> 1) & 1u;   // same stage / S buffer as step j
+          const bool has_next = (j + 1 < it.je), has_next2 = (j + 2 < it.je);
           mbar_wait(&ds_ready, kv_iter & 1u, ab);
           tc_fence_after();
           issue_ts(TM_DQ, TM_DP, k_base + st * TILE_BYTES, j > it.jb);
@@ -494,6 +496,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             umma_commit(&dp_full);
             umma_commit(&v_empty[st_n]);
           }
+          if (has_next2) {
+            mbar_wait(&k_full[st], ph_n2, ab);
+            tc_fence_after();
+            issue_kk(TM_S + st * 128u, q_base, k_base + st * TILE_BYTES);
+            umma_commit(&s_full[st]);
+          }
+          // every product that reads Q / dO has been issued: the next item's tiles may come in
+          // while the remaining dQ products and the epilogue run
+          if (has_next ? !has_next2 : n_kt == 1) umma_commit(&qdo_free);
         }
         umma_commit(&acc_done);
         ring_release(ring, n_ring);
