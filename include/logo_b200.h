@@ -211,6 +211,18 @@ int logo_fuse_bwd(const void* d_out, const void* local, const void* glob, const 
                   int d, float eps, int use_norm, void* workspace, size_t workspace_bytes, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Rotary position embedding. Replaces apply_rotary_pos_emb (logo/modules/rotary.py:81-106, rotate_half :81-85) as
+ * called at logo/layers/logo.py:136-139 for both branches:
+ *     out = (x * cos) + (rotate_half(x) * sin)
+ * with the three bf16 roundings of that eager expression, in one pass.
+ *   x, out [n_tokens, heads, 128] bf16 (out may alias x); cos, sin [n_tokens, 128] bf16
+ *   inverse != 0 applies the transposed rotation: the gradient with respect to x of the
+ *   expression above, given the output gradient in `x`.
+ * ------------------------------------------------------------------------------------------ */
+int logo_rope(const void* x, void* out, const void* cos, const void* sin, int n_tokens, int heads, int d,
+              int inverse, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * KV cache (bf16, head-major):
  *   global branch: k_cache, v_cache [batch, h, t_max, 128]; token p of a sequence sits at row p
  *   local branch : k_ring,  v_ring  [batch, h, ring, 128];  token p sits at row p % ring

@@ -227,8 +227,14 @@ class LoGoAttention(nn.Module):
             cos, sin = self.rotary_emb(v_l, position_ids)
         else:
             cos, sin = position_embeddings
-        q_l, k_l = apply_rotary_pos_emb(q_l, k_l, cos, sin, unsqueeze_dim=2)
-        q_g, k_g = apply_rotary_pos_emb(q_g, k_g, cos, sin, unsqueeze_dim=2)
+        # rotary embedding of both branches (logo/layers/logo.py:136-139): one kernel per tensor
+        n_tok = bsz * q_len
+        cos2 = cos.reshape(n_tok, D).to(torch.bfloat16)
+        sin2 = sin.reshape(n_tok, D).to(torch.bfloat16)
+        q_l = ops.rope(q_l.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
+        k_l = ops.rope(k_l.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
+        q_g = ops.rope(q_g.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
+        k_g = ops.rope(k_g.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
 
         scale = D ** -0.5
         is_decode = past_key_value is not None and q_len == 1

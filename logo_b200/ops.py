@@ -322,6 +322,44 @@ def sdpa_causal_ref(q, k, v, scale=None, cu_seqlens=None):
 
 
 # ----------------------------------------------------------------------------------------
+# rotary position embedding (logo/modules/rotary.py:81-106, used at logo/layers/logo.py:136-139)
+# ----------------------------------------------------------------------------------------
+def _rope_call(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool) -> torch.Tensor:
+    lib = _lib.load()
+    n, h, d = x.shape
+    out = torch.empty_like(x)
+    rc = lib.logo_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, h, d, int(inverse),
+                       _lib.current_stream_ptr(x.device))
+    _lib.check(rc, "logo_rope")
+    return out
+
+
+class RopeFunction(torch.autograd.Function):
+    """``(x * cos) + (rotate_half(x) * sin)`` on packed ``[N, H, 128]`` bf16 rows, one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        _require_cuda(x, cos, sin)
+        if x.dtype != torch.bfloat16 or cos.dtype != torch.bfloat16 or sin.dtype != torch.bfloat16:
+            raise TypeError("the rotary kernel takes bf16 activations and bf16 cos / sin tables")
+        if x.dim() != 3 or cos.shape != (x.shape[0], x.shape[2]) or sin.shape != cos.shape:
+            raise ValueError("rope: x must be [N, H, D] and cos / sin [N, D]")
+        x, cos, sin = x.contiguous(), cos.contiguous(), sin.contiguous()
+        ctx.save_for_backward(cos, sin)
+        return _rope_call(x, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        cos, sin = ctx.saved_tensors
+        return _rope_call(d_out.contiguous(), cos, sin, True), None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x [N, H, 128]`` with per-token tables ``cos, sin [N, 128]`` (all bf16)."""
+    return RopeFunction.apply(x, cos, sin)
+
+
+# ----------------------------------------------------------------------------------------
 # per-branch RMSNorm + gate mask + blend (logo/layers/logo.py:180-182,225-227,256-258)
 # ----------------------------------------------------------------------------------------
 class FuseFunction(torch.autograd.Function):

@@ -104,3 +104,16 @@ def layer_case_inputs(case):
         cu = None
         pos = np.broadcast_to(np.arange(t, dtype=np.int64)[None], (b, t)).copy()
     return hidden, cu, pos
+
+
+# ----------------------------------------------------------------------------------------------
+# rotary embedding (bf16 eager graph of logo/modules/rotary.py:81-106)
+# ----------------------------------------------------------------------------------------------
+def rope_case():
+    """x [N, H, D], output gradient g [N, H, D], positions [N] (fp32 arrays; the users round to bf16)."""
+    rs = np.random.RandomState(11)
+    n, h, d = 96, 3, 128
+    x = rs.standard_normal((n, h, d)).astype(np.float32)
+    g = rs.standard_normal((n, h, d)).astype(np.float32)
+    pos = rs.randint(0, 8192, size=n).astype(np.int64)
+    return x, g, pos

@@ -246,11 +246,34 @@ def gen_misc():
     print("misc.npz")
 
 
+def gen_rope():
+    """The reference's rotary embedding on bf16 tensors (its eager rounding sequence) and the gradient
+    autograd gives for it; tables from the reference's RotaryEmbedding."""
+    from logo.modules.rotary import apply_rotary_pos_emb
+    from golden_inputs import rope_case
+    x, g, pos = rope_case()
+    n, h, d = x.shape
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
+    fr = torch.from_numpy(pos).float()[:, None] * inv[None, :]
+    emb = torch.cat([fr, fr], dim=-1)
+    cos, sin = emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)       # [N, D]
+    # reference layout: q [B, heads, T, D] with cos [B, T, D] broadcast over heads (unsqueeze_dim=1)
+    q = torch.from_numpy(x).to(torch.bfloat16).permute(1, 0, 2)[None].contiguous().requires_grad_(True)
+    k = q.detach().clone()
+    q_out, _ = apply_rotary_pos_emb(q, k, cos[None], sin[None])
+    q_out.backward(torch.from_numpy(g).to(torch.bfloat16).permute(1, 0, 2)[None].contiguous())
+    out = {"cos": cos.float().numpy(), "sin": sin.float().numpy(),
+           "out": q_out.detach()[0].permute(1, 0, 2).float().numpy(),
+           "grad": q.grad[0].permute(1, 0, 2).float().numpy()}
+    np.savez_compressed(OUT / "rope.npz", **out)
+    print("rope.npz")
+
+
 if __name__ == "__main__":
+    import sys
     torch.set_num_threads(8)
     install_shims()
-    gen_selection()
-    gen_attention()
-    gen_layer()
-    gen_decode()
-    gen_misc()
+    gens = {"selection": gen_selection, "attention": gen_attention, "layer": gen_layer, "decode": gen_decode,
+            "misc": gen_misc, "rope": gen_rope}
+    for name in (sys.argv[1:] or list(gens)):       # `make_golden.py rope` regenerates one fixture only
+        gens[name]()

@@ -140,3 +140,18 @@ def test_update_gate_thres_matches_reference(golden):
     np.testing.assert_allclose(thres, g["update/thres"], atol=1e-7)
     np.testing.assert_allclose(ratio, g["update/ratio"].reshape(-1), atol=1e-7)
     assert np.all(g["update/counters"] == 0)
+
+
+def test_rope_bf16_graph_bit_exact(golden):
+    """The oracle's rotary embedding on bf16 tensors reproduces the reference's eager bf16 graph and
+    the gradient autograd gives for it."""
+    from golden_inputs import rope_case
+
+    g = golden["rope"]
+    x, grad_out, _ = rope_case()
+    cos, sin = torch.from_numpy(g["cos"]).to(torch.bfloat16), torch.from_numpy(g["sin"]).to(torch.bfloat16)
+    xt = torch.from_numpy(x).to(torch.bfloat16).requires_grad_(True)
+    out = orc.apply_rope(xt, cos, sin)
+    out.backward(torch.from_numpy(grad_out).to(torch.bfloat16))
+    np.testing.assert_array_equal(out.detach().float().numpy(), g["out"])
+    np.testing.assert_array_equal(xt.grad.float().numpy(), g["grad"])
