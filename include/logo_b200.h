@@ -215,12 +215,14 @@ int logo_fuse_bwd(const void* d_out, const void* local, const void* glob, const 
  * called at logo/layers/logo.py:136-139 for both branches:
  *     out = (x * cos) + (rotate_half(x) * sin)
  * with the three bf16 roundings of that eager expression, in one pass.
- *   x, out [n_tokens, heads, 128] bf16 (out may alias x); cos, sin [n_tokens, 128] bf16
+ *   x: bf16 rows of 128, row (token t, head h) at x + t * x_stride_tok + h * x_stride_head (element
+ *      strides, multiples of 8); out [n_tokens, heads, 128] bf16 packed (may alias a packed x);
+ *   cos, sin [n_tokens, 128] bf16
  *   inverse != 0 applies the transposed rotation: the gradient with respect to x of the
  *   expression above, given the output gradient in `x`.
  * ------------------------------------------------------------------------------------------ */
-int logo_rope(const void* x, void* out, const void* cos, const void* sin, int n_tokens, int heads, int d,
-              int inverse, logo_stream_t stream);
+int logo_rope(const void* x, long long x_stride_tok, long long x_stride_head, void* out, const void* cos,
+              const void* sin, int n_tokens, int heads, int d, int inverse, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * KV cache (bf16, head-major):

@@ -10,7 +10,9 @@
 //
 // Layout: eight lanes own one 128-element head row; a lane loads the 16-byte chunk at column
 // 8*l of the first half together with its partner at column 64 + 8*l, so both halves of a rotation
-// pair sit in one thread. cos / sin are [n_tokens, 128] (any values: the two halves are read
+// pair sit in one thread. The input may be any view with contiguous 128-element rows (token and
+// head strides are arguments: the per-head projection of the global branch comes out head-major);
+// the output is packed. cos / sin are [n_tokens, 128] (any values: the two halves are read
 // separately, nothing assumes cos[d] == cos[d + 64]).
 // Bytes per token: heads * 256 read + heads * 256 written (+ 512 for cos / sin, L1-resident across
 // the heads of a token).
@@ -43,12 +45,13 @@ template <bool INVERSE>
 __global__ void __launch_bounds__(ROPE_THREADS)
     rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                 const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t, long long n_rows,
-                int heads) {
+                int heads, long long x_stride_tok, long long x_stride_head) {
   const long long stride = (long long)gridDim.x * (ROPE_THREADS / 8);
   const int l = threadIdx.x & 7;
   for (long long row = (long long)blockIdx.x * (ROPE_THREADS / 8) + (threadIdx.x >> 3); row < n_rows; row += stride) {
     const long long tok = row / heads;
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * 128);
+    const int head = (int)(row - tok * heads);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + tok * x_stride_tok + head * x_stride_head);
     const uint4* cr = reinterpret_cast<const uint4*>(cos_t + tok * 128);
     const uint4* sr = reinterpret_cast<const uint4*>(sin_t + tok * 128);
     const uint4 vx1 = __ldcs(xr + l), vx2 = __ldcs(xr + 8 + l);
@@ -81,13 +84,16 @@ __global__ void __launch_bounds__(ROPE_THREADS)
 
 }  // namespace logo
 
-extern "C" int logo_rope(const void* x, void* out, const void* cos_t, const void* sin_t, int n_tokens, int heads,
-                         int d, int inverse, logo_stream_t stream) {
+extern "C" int logo_rope(const void* x, long long x_stride_tok, long long x_stride_head, void* out, const void* cos_t,
+                         const void* sin_t, int n_tokens, int heads, int d, int inverse, logo_stream_t stream) {
   using namespace logo;
   LOGO_REQUIRE(d == 128, LOGO_ERR_UNSUPPORTED, "rope: head_dim must be 128");
   LOGO_REQUIRE(n_tokens >= 0 && heads > 0, LOGO_ERR_INVALID, "rope: bad sizes");
   if (n_tokens == 0) return LOGO_OK;
   LOGO_REQUIRE(x && out && cos_t && sin_t, LOGO_ERR_INVALID, "rope: NULL pointer");
+  LOGO_REQUIRE(x_stride_tok % 8 == 0 && x_stride_head % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               LOGO_ERR_INVALID, "rope: rows must be 16-byte aligned (strides multiples of 8 elements)");
   const long long n_rows = (long long)n_tokens * heads;
   const long long want = (n_rows + (ROPE_THREADS / 8) - 1) / (ROPE_THREADS / 8);
   const int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
@@ -95,11 +101,11 @@ extern "C" int logo_rope(const void* x, void* out, const void* cos_t, const void
   if (inverse)
     rope_kernel<true><<<grid, ROPE_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
                                                     (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, n_rows,
-                                                    heads);
+                                                    heads, x_stride_tok, x_stride_head);
   else
     rope_kernel<false><<<grid, ROPE_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
                                                      (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, n_rows,
-                                                     heads);
+                                                     heads, x_stride_tok, x_stride_head);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
 }

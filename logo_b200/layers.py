@@ -184,10 +184,12 @@ class LoGoAttention(nn.Module):
         q_view = q.view(bsz, q_len, self.num_heads, self.head_dim)
         k_view = k.view(bsz, q_len, self.num_key_value_heads, self.head_dim)
         v_view = v.view(bsz, q_len, self.num_key_value_heads, self.head_dim)
+        # [B, L, H, E] results (views of the head-major buffers the batched product writes): the rotary
+        # kernel reads q / k through their strides, only v is packed here
         q_out = torch.einsum("b l h d, h d e -> b l h e", q_view, self.q_global_proj)
         k_out = torch.einsum("b l h d, h d e -> b l h e", k_view, self.k_global_proj)
         v_out = torch.einsum("b l h d, h d e -> b l h e", v_view, self.v_global_proj)
-        return q_out.reshape(bsz, q_len, -1), k_out.reshape(bsz, q_len, -1), v_out.reshape(bsz, q_len, -1)
+        return q_out, k_out, v_out.reshape(bsz, q_len, -1)
 
     # -- forward -----------------------------------------------------------------------------------
     def forward(
@@ -221,7 +223,7 @@ class LoGoAttention(nn.Module):
         q_l = query_states.view(bsz, q_len, H, D)
         k_l = key_states.view(bsz, q_len, HKV, D)
         v_l = value_states.view(bsz, q_len, HKV, D)
-        q_g, k_g, v_g = gq.view(bsz, q_len, H, D), gk.view(bsz, q_len, HKV, D), gv.view(bsz, q_len, HKV, D)
+        q_g, k_g, v_g = gq.reshape(bsz, q_len, H, D), gk.reshape(bsz, q_len, HKV, D), gv.view(bsz, q_len, HKV, D)
 
         if position_embeddings is None:
             cos, sin = self.rotary_emb(v_l, position_ids)

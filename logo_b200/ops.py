@@ -327,9 +327,11 @@ def sdpa_causal_ref(q, k, v, scale=None, cu_seqlens=None):
 def _rope_call(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool) -> torch.Tensor:
     lib = _lib.load()
     n, h, d = x.shape
-    out = torch.empty_like(x)
-    rc = lib.logo_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, h, d, int(inverse),
-                       _lib.current_stream_ptr(x.device))
+    if x.stride(2) != 1 or x.stride(0) % 8 or x.stride(1) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()      # rows must be contiguous and 16-byte aligned; any token / head strides are fine
+    out = torch.empty((n, h, d), dtype=x.dtype, device=x.device)
+    rc = lib.logo_rope(x.data_ptr(), x.stride(0), x.stride(1), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, h, d,
+                       int(inverse), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "logo_rope")
     return out
 
@@ -344,14 +346,14 @@ class RopeFunction(torch.autograd.Function):
             raise TypeError("the rotary kernel takes bf16 activations and bf16 cos / sin tables")
         if x.dim() != 3 or cos.shape != (x.shape[0], x.shape[2]) or sin.shape != cos.shape:
             raise ValueError("rope: x must be [N, H, D] and cos / sin [N, D]")
-        x, cos, sin = x.contiguous(), cos.contiguous(), sin.contiguous()
+        cos, sin = cos.contiguous(), sin.contiguous()
         ctx.save_for_backward(cos, sin)
         return _rope_call(x, cos, sin, False)
 
     @staticmethod
     def backward(ctx, d_out):
         cos, sin = ctx.saved_tensors
-        return _rope_call(d_out.contiguous(), cos, sin, True), None, None
+        return _rope_call(d_out, cos, sin, True), None, None
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

@@ -67,12 +67,27 @@ def test_rope_in_place_and_empty(cuda_device):
     cos, sin = _tables(64, 128, 1)
     want = orc.apply_rope(x, cos, sin)
     xd, cd, sd = x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device)
-    rc = lib.logo_rope(xd.data_ptr(), xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), 64, 2, 128, 0, None)
+    rc = lib.logo_rope(xd.data_ptr(), 256, 128, xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), 64, 2, 128, 0, None)
     assert rc == 0
     torch.cuda.synchronize()
     assert torch.equal(xd.cpu().view(torch.int16), want.view(torch.int16))
-    assert lib.logo_rope(None, None, None, None, 0, 2, 128, 0, None) == 0
-    assert lib.logo_rope(xd.data_ptr(), xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), 64, 2, 64, 0, None) != 0
+    assert lib.logo_rope(None, 256, 128, None, None, None, 0, 2, 128, 0, None) == 0
+    assert lib.logo_rope(xd.data_ptr(), 256, 128, xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), 64, 2, 64, 0, None) != 0
+    assert lib.logo_rope(xd.data_ptr(), 252, 128, xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), 64, 2, 128, 0, None) != 0
+
+
+def test_rope_head_major_input_view(cuda_device):
+    """The global branch's per-head projection comes out as a [H, N, D] buffer viewed [N, H, D]."""
+    from logo_b200 import ops
+
+    torch.manual_seed(21)
+    n, h = 130, 4
+    buf = torch.randn(h, n, 128).to(torch.bfloat16)
+    cos, sin = _tables(n, 128, 8)
+    want = orc.apply_rope(buf.permute(1, 0, 2), cos, sin)
+    got = ops.rope(buf.to(cuda_device).permute(1, 0, 2), cos.to(cuda_device), sin.to(cuda_device))
+    assert got.is_contiguous()
+    assert torch.equal(got.cpu().view(torch.int16), want.contiguous().view(torch.int16))
 
 
 def test_rope_against_reference_fixture(cuda_device, golden):
