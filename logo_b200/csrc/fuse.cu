@@ -64,6 +64,38 @@ __device__ __forceinline__ void load_weight8(const void* w, int w_dtype, int col
   }
 }
 
+// The eager graph does its bf16 element-wise arithmetic one operation at a time, each rounded to
+// bf16. A bf16 x bf16 product is exact in fp32, and an fp32 sum of two bf16 values rounds to the same
+// bf16 as the exact sum, so the packed bf16 instructions (one rounding of the exact result) give the
+// graph's bits at a quarter of the instruction count of convert / multiply / convert. The `_rn`
+// forms are required: the plain ones may be contracted into a fused multiply-add, which skips the
+// rounding of the product.
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bsplat2(float x) { return pack_bf16x2(x, x); }
+
+// normalised row as packed bf16 (`hidden_states.to(input_dtype)`): four words for eight elements
+__device__ __forceinline__ void normalise8_packed(const uint4& v, float eps, uint32_t (&xh)[4]) {
+  float x[8];
+  unpack8(v, x);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  const float rstd = rsqrtf(ss * (1.0f / FUSE_D) + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) xh[i] = pack_bf16x2(x[2 * i] * rstd, x[2 * i + 1] * rstd);
+}
+
 // sum over the 16 lanes that share a row
 __device__ __forceinline__ float row_sum16(float x) {
   x += __shfl_xor_sync(0xffffffffu, x, 8);
@@ -105,6 +137,12 @@ __global__ void __launch_bounds__(FUSE_THREADS)
   float wl[8], wg[8];
   load_weight8(use_norm ? w_local : nullptr, w_dtype, col, wl);
   load_weight8(use_norm ? w_global : nullptr, w_dtype, col, wg);
+  uint32_t wl2[4], wg2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    wl2[i] = pack_bf16x2(wl[2 * i], wl[2 * i + 1]);
+    wg2[i] = pack_bf16x2(wg[2 * i], wg[2 * i + 1]);
+  }
 
   for (int tok = blockIdx.x * warps_per_block + (threadIdx.x >> 5); tok < n_tokens;
        tok += gridDim.x * warps_per_block) {
@@ -112,6 +150,7 @@ __global__ void __launch_bounds__(FUSE_THREADS)
     const bool selected = gate_f >= thres;
     const float g = selected ? gate_f : 0.f;
     const float one_minus_g = bf16_round(1.f - g);
+    const uint32_t g2 = bsplat2(g), omg2 = bsplat2(one_minus_g);
     // FUSE_U head pairs per iteration: all their loads are issued before the first reduction, which
     // is what keeps enough bytes in flight. The trip count is warp-uniform (the row sums shuffle).
     for (int hb = 0; hb < h; hb += 2 * FUSE_U) {
@@ -125,6 +164,26 @@ __global__ void __launch_bounds__(FUSE_THREADS)
         off[u] = ((size_t)tok * h + (act[u] ? hh : 0)) * FUSE_D + col;
         lv[u] = __ldg(reinterpret_cast<const uint4*>(local + off[u]));
         if (selected) gv[u] = __ldg(reinterpret_cast<const uint4*>(glob + off[u]));
+      }
+      if (use_norm && bf16_w) {
+        // bf16 weights (the layer's own dtype): everything after the normalisation is packed bf16
+#pragma unroll
+        for (int u = 0; u < FUSE_U; ++u) {
+          uint32_t xh[4], yl[4];
+          normalise8_packed(lv[u], eps, xh);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) yl[i] = bmul2(wl2[i], xh[i]);
+          if (selected) {
+            uint32_t yg[4];
+            normalise8_packed(gv[u], eps, xh);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) yg[i] = bmul2(wg2[i], xh[i]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) yl[i] = badd2(bmul2(omg2, yl[i]), bmul2(g2, yg[i]));
+          }
+          if (act[u]) *reinterpret_cast<uint4*>(out + off[u]) = make_uint4(yl[0], yl[1], yl[2], yl[3]);
+        }
+        continue;
       }
 #pragma unroll
       for (int u = 0; u < FUSE_U; ++u) {
@@ -153,7 +212,7 @@ __global__ void __launch_bounds__(FUSE_THREADS)
 
 // Backward. Each warp owns tokens; the weight gradients are accumulated per thread, reduced
 // per block in a fixed order and written as block partials; fuse_bwd_finish_kernel sums them.
-__global__ void __launch_bounds__(FUSE_THREADS)
+__global__ void __launch_bounds__(FUSE_THREADS, 3)   // three blocks per SM: the kernel is latency-bound
     fuse_bwd_kernel(const __nv_bfloat16* __restrict__ d_out, const __nv_bfloat16* __restrict__ local,
                     const __nv_bfloat16* __restrict__ glob, const __nv_bfloat16* __restrict__ gate,
                     const void* __restrict__ thres_ptr, int thres_dtype, const void* __restrict__ w_local,
@@ -268,18 +327,39 @@ __global__ void __launch_bounds__(FUSE_THREADS)
   }
 }
 
-__global__ void __launch_bounds__(256)
+// Sums the block partials in a fixed order: 4 slices of the block list per column in parallel, then
+// the 4 slice sums in order (deterministic, and 4x shorter than one thread per column walking the list).
+__global__ void __launch_bounds__(1024)
     fuse_bwd_finish_kernel(const float* __restrict__ partials, int nblocks, void* d_w_local, void* d_w_global,
                            int w_dtype) {
-  const int which = threadIdx.x >> 7, c = threadIdx.x & 127;
+  __shared__ float s_acc[4][2 * FUSE_D];
+  const int slice = threadIdx.x >> 8, wc = threadIdx.x & 255;   // wc = which * 128 + column
+  const int per = (nblocks + 3) / 4;
+  const int b0 = slice * per, b1 = min(b0 + per, nblocks);
   float acc = 0.f;
-  for (int b = 0; b < nblocks; ++b) acc += partials[((size_t)b * 2 + which) * FUSE_D + c];
-  void* dst = which == 0 ? d_w_local : d_w_global;
-  if (!dst) return;
-  if (w_dtype == LOGO_DTYPE_BF16)
-    static_cast<__nv_bfloat16*>(dst)[c] = __float2bfloat16_rn(acc);
-  else
-    static_cast<float*>(dst)[c] = acc;
+  int b = b0;
+  for (; b + 8 <= b1; b += 8) {   // eight loads in flight, added in list order
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = __ldg(partials + (size_t)(b + k) * 2 * FUSE_D + wc);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += v[k];
+  }
+  for (; b < b1; ++b) acc += __ldg(partials + (size_t)b * 2 * FUSE_D + wc);
+  s_acc[slice][wc] = acc;
+  __syncthreads();
+  if (slice == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tot += s_acc[k][wc];
+    void* dst = (wc >> 7) == 0 ? d_w_local : d_w_global;
+    if (!dst) return;
+    const int c = wc & 127;
+    if (w_dtype == LOGO_DTYPE_BF16)
+      static_cast<__nv_bfloat16*>(dst)[c] = __float2bfloat16_rn(tot);
+    else
+      static_cast<float*>(dst)[c] = tot;
+  }
 }
 
 static int fuse_grid(int n_tokens) {
@@ -360,7 +440,7 @@ extern "C" int logo_fuse_bwd(const void* d_out, const void* local, const void* g
     LOGO_CHECK_CUDA(cudaGetLastError());
   }
   if (use_norm && (d_w_local || d_w_global)) {
-    fuse_bwd_finish_kernel<<<1, 256, 0, stream>>>(static_cast<const float*>(workspace), grid, d_w_local, d_w_global,
+    fuse_bwd_finish_kernel<<<1, 1024, 0, stream>>>(static_cast<const float*>(workspace), grid, d_w_local, d_w_global,
                                                   w_dtype);
     LOGO_CHECK_CUDA(cudaGetLastError());
   }

@@ -19,26 +19,11 @@
 #include "host_common.cuh"
 #include "ptx.cuh"
 
+#include <cuda_bf16.h>
+
 namespace logo {
 
 constexpr int ROPE_THREADS = 256;
-
-__device__ __forceinline__ float rope_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-
-__device__ __forceinline__ void rope_unpack8(const uint4& v, float (&f)[8]) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-__device__ __forceinline__ uint4 rope_pack8(const float (&f)[8]) {
-  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
-                    pack_bf16x2(f[6], f[7]));
-}
 
 // One thread: columns [8*l, 8*l+8) and [64 + 8*l, 64 + 8*l + 8) of one (token, head) row.
 template <bool INVERSE>
@@ -57,28 +42,34 @@ __global__ void __launch_bounds__(ROPE_THREADS)
     const uint4 vx1 = __ldcs(xr + l), vx2 = __ldcs(xr + 8 + l);
     const uint4 vc1 = __ldg(cr + l), vc2 = __ldg(cr + 8 + l);
     const uint4 vs1 = __ldg(sr + l), vs2 = __ldg(sr + 8 + l);
-    float x1[8], x2[8], c1[8], c2[8], s1[8], s2[8], o1[8], o2[8];
-    rope_unpack8(vx1, x1);
-    rope_unpack8(vx2, x2);
-    rope_unpack8(vc1, c1);
-    rope_unpack8(vc2, c2);
-    rope_unpack8(vs1, s1);
-    rope_unpack8(vs2, s2);
+    // Packed bf16 arithmetic: a bf16 x bf16 product is exact in fp32 and an fp32 sum of two bf16
+    // values rounds to the same bf16 as their exact sum, so one rounding per packed instruction
+    // reproduces the eager graph's convert / multiply / convert sequence bit for bit (`_rn` forms:
+    // the plain ones may be contracted into a fused multiply-add, losing the product's rounding).
+    const __nv_bfloat162* x1 = reinterpret_cast<const __nv_bfloat162*>(&vx1);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&vx2);
+    const __nv_bfloat162* c1 = reinterpret_cast<const __nv_bfloat162*>(&vc1);
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&vc2);
+    const __nv_bfloat162* s1 = reinterpret_cast<const __nv_bfloat162*>(&vs1);
+    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&vs2);
+    uint4 w1, w2;
+    __nv_bfloat162* o1 = reinterpret_cast<__nv_bfloat162*>(&w1);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&w2);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       if (!INVERSE) {
         // first half: x1*cos1 + (-x2)*sin1 ; second half: x2*cos2 + x1*sin2
-        o1[i] = rope_round(rope_round(x1[i] * c1[i]) + rope_round(-x2[i] * s1[i]));
-        o2[i] = rope_round(rope_round(x2[i] * c2[i]) + rope_round(x1[i] * s2[i]));
+        o1[i] = __hadd2_rn(__hmul2_rn(x1[i], c1[i]), __hmul2_rn(__hneg2(x2[i]), s1[i]));
+        o2[i] = __hadd2_rn(__hmul2_rn(x2[i], c2[i]), __hmul2_rn(x1[i], s2[i]));
       } else {
         // gradient: y*cos + rotate_half^T(y*sin), rotate_half^T(z) = cat(z[64:], -z[:64])
-        o1[i] = rope_round(rope_round(x1[i] * c1[i]) + rope_round(x2[i] * s2[i]));
-        o2[i] = rope_round(rope_round(x2[i] * c2[i]) + (-rope_round(x1[i] * s1[i])));
+        o1[i] = __hadd2_rn(__hmul2_rn(x1[i], c1[i]), __hmul2_rn(x2[i], s2[i]));
+        o2[i] = __hadd2_rn(__hmul2_rn(x2[i], c2[i]), __hneg2(__hmul2_rn(x1[i], s1[i])));
       }
     }
     uint4* orow = reinterpret_cast<uint4*>(out + row * 128);
-    __stcs(orow + l, rope_pack8(o1));
-    __stcs(orow + 8 + l, rope_pack8(o2));
+    __stcs(orow + l, w1);
+    __stcs(orow + 8 + l, w2);
   }
 }
 
