@@ -346,9 +346,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           ds_pack_chunk_row(p0, d0, delta_r, pk);
           ds_pack_chunk_row(p1, d1, delta_r, pk + 16);
         }
-        // every warp has finished reading dP before anyone overwrites it with dS
-        named_barrier_sync(1, 256);
-        tmem_st32(TM_DP + lane_off + (uint32_t)(half * 32), pk);
+        // dS (bf16) goes into the first 32 of the 64 dP columns this warp has just read: no other warp
+        // reads or writes them, so no barrier is needed before the overwrite
+        tmem_st32(TM_DP + lane_off + (uint32_t)col0, pk);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&ds_ready);
@@ -443,7 +443,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                                      idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-        umma_tile_k128<true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
+        umma_tile_k128<true, true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+                                         acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
@@ -731,8 +732,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           uint32_t pk[32];
           pack_chunk(p0, pk);
           pack_chunk(p1, pk + 16);
-          named_barrier_sync(1, 256);   // all reads of S^T done before P^T overwrites it
-          tmem_st32(TM_ST + lane_off + (uint32_t)(half * 32), pk);
+          // P^T (bf16) overwrites the first 32 of the 64 S^T columns this warp has just read: private
+          // to the warp, no barrier needed
+          tmem_st32(TM_ST + lane_off + (uint32_t)col0, pk);
           tmem_st_wait();
           tc_fence_before();
           mbar_arrive(&p_ready);
@@ -753,8 +755,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             cp_async_wait_all();
             if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
           }
-          named_barrier_sync(2, 256);   // all reads of dP^T done; next step's vectors visible
-          tmem_st32(TM_DPT + lane_off + (uint32_t)(half * 32), pk);
+          named_barrier_sync(2, 256);   // vector buffers: this step.s reads done, next step.s values visible
+          tmem_st32(TM_DPT + lane_off + (uint32_t)col0, pk);
           tmem_st_wait();
           tc_fence_before();
           mbar_arrive(&ds_ready);
@@ -863,7 +865,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                                      idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-        umma_tile_k128<true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
+        umma_tile_k128<true, true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+                                         acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {

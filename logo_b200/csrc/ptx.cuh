@@ -251,7 +251,10 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 //   A_TMEM: A comes from tensor memory (8 columns per k-step), else from K-major 128B-swizzled
 //           shared memory (two [128][64] blocks: 32 bytes per k-step, 16 KB between the blocks);
 //   B_MN  : B is MN-major ([k][n] rows as they lie in memory, 2 KB per k-step), else K-major.
-template <bool A_TMEM, bool B_MN>
+//   A_SPLIT (with A_TMEM): the second half of the k range (k-steps 4-7) starts 64 columns after the
+//           first instead of 32: each half of A then lies inside the 64 fp32 columns it was computed
+//           from, so the warps that produce the two halves never touch each other's columns.
+template <bool A_TMEM, bool B_MN, bool A_SPLIT = false>
 __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
                                                uint32_t accumulate_first) {
   if (elect_one()) {
@@ -268,7 +271,8 @@ __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uin
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
             "}\n"
             :
-            : "r"(d_tmem), "r"((uint32_t)a0 + (uint32_t)kk * 8u), "l"(b), "r"(idesc), "r"(acc)
+            : "r"(d_tmem), "r"((uint32_t)a0 + (uint32_t)kk * 8u + ((A_SPLIT && kk >= 4) ? 32u : 0u)), "l"(b), "r"(idesc),
+              "r"(acc)
             : "memory");
       } else {
         asm volatile(
