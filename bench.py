@@ -276,6 +276,26 @@ def run_gpu(args):
         "bwd_dq": 1.5 * f_fwd / (kernel_ms["bwd_dq"] * 1e-3) / 1e12 if kernel_ms["bwd_dq"] else None,
     }
 
+    # the other ratios of the configuration's sweep (same step, 5 timed steps each; not the headline)
+    sweep = {f"{args.ratio:g}": round(value / world, 1)}
+    if not args.skip_e2e:
+        for r in (0.125, 0.25, 0.5, 1.0):
+            if abs(r - args.ratio) < 1e-9:
+                continue
+            b2 = make_batch(device, r, seed=99)
+            f2 = 3.5 * effective_flops_fwd(b2[4])
+            for _ in range(2):
+                device_step(b2)
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(5):
+                device_step(b2)
+            s1.record()
+            torch.cuda.synchronize()
+            sweep[f"{r:g}"] = round(f2 * 5 / (s0.elapsed_time(s1) * 1e-3) / 1e12, 1)
+            del b2
+
     if args.skip_cpu:
         cpu_value, cpu_ms, cores = None, float("nan"), 0
     else:
@@ -295,6 +315,7 @@ def run_gpu(args):
         "roofline": roofline,
         "kernel_ms": kernel_ms, "kernel_tflops": kernel_tflops,
         "frac_of_peak_fwd_bwd": value / world / peaks["bf16"],
+        "ratio_sweep_tflops_rank0": sweep,
         "cpu_baseline": {"value": cpu_value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": "oracle fwd+bwd on 1 sequence x 2048 tokens x 4 heads, fp32, 3 steps "
                                    f"({cpu_ms:.0f} ms each)"},

@@ -45,7 +45,9 @@ struct BwdArgs {
   int* status;
 };
 
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 320;      // dK/dV kernel: 8 element-wise warps + producer + MMA
+constexpr int DQ_EW_WARPS = 16;        // dQ kernel: 16 element-wise warps (four per scheduler), 32 columns each
+constexpr int DQ_THREADS = (DQ_EW_WARPS + 2) * 32;
 constexpr int BWD_SMEM_BYTES = 6 * TILE_BYTES + 1024;
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
@@ -160,7 +162,10 @@ __global__ void __launch_bounds__(256)
   const int sq = gathered ? min(max(__ldg(sq_ptr), 0), n_tokens) : n_tokens;
   const int rows_total = gathered ? min(sq + TILE, cap) : sq;
   const int lane = threadIdx.x & 31;
+  const int sub = lane >> 4;            // which of the two heads a warp handles at a time
+  const int col = (lane & 15) * 8;      // 16 lanes x 16 bytes cover one 128-element row
   const int warps_per_block = blockDim.x >> 5;
+  constexpr int U = 4;                  // head pairs in flight: all their loads are issued before the first reduction
   for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < rows_total; r += gridDim.x * warps_per_block) {
     if (r < sq) {
       long long tok = gathered ? __ldg(q_idx + r) : (long long)r;
@@ -168,41 +173,60 @@ __global__ void __launch_bounds__(256)
         if (lane == 0 && status) atomicCAS(status, 0, (int)DEV_BAD_INDEX);
         tok = 0;
       }
-      for (int hh = 0; hh < hq; ++hh) {
-        const size_t src = ((size_t)tok * hq + hh) * HEAD_DIM + lane * 4;
-        const uint2 ov = __ldg(reinterpret_cast<const uint2*>(o + src));
-        const uint2 dv = __ldg(reinterpret_cast<const uint2*>(d_o + src));
-        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
-        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
-        float acc = 0.f;
+      for (int hb = 0; hb < hq; hb += 2 * U) {
+        uint4 ov[U], dv[U], qv[U];
+        float lv[U];
+        bool act[U];
+        int hh[U];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const float2 of = __bfloat1622float2(o2[i]);
-          const float2 df = __bfloat1622float2(d2[i]);
-          acc = fmaf(of.x, df.x, acc);
-          acc = fmaf(of.y, df.y, acc);
+        for (int u = 0; u < U; ++u) {
+          hh[u] = hb + 2 * u + sub;
+          act[u] = hh[u] < hq;
+          const size_t src = ((size_t)tok * hq + (act[u] ? hh[u] : 0)) * HEAD_DIM + col;
+          ov[u] = __ldg(reinterpret_cast<const uint4*>(o + src));
+          dv[u] = __ldg(reinterpret_cast<const uint4*>(d_o + src));
+          if (gathered) qv[u] = __ldg(reinterpret_cast<const uint4*>(q + src));
+          lv[u] = __ldg(lse + (size_t)tok * hq + (act[u] ? hh[u] : 0));
         }
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) {
-          delta_sel[(size_t)hh * cap + r] = acc;
-          lse_sel[(size_t)hh * cap + r] = __ldg(lse + (size_t)tok * hq + hh);
-        }
-        if (gathered) {
-          const size_t dst = ((size_t)r * hq + hh) * HEAD_DIM + lane * 4;
-          *reinterpret_cast<uint2*>(q_sel + dst) = __ldg(reinterpret_cast<const uint2*>(q + src));
-          *reinterpret_cast<uint2*>(do_sel + dst) = dv;
+        for (int u = 0; u < U; ++u) {
+          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov[u]);
+          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[u]);
+          float acc = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 of = __bfloat1622float2(o2[i]);
+            const float2 df = __bfloat1622float2(d2[i]);
+            acc = fmaf(of.x, df.x, acc);
+            acc = fmaf(of.y, df.y, acc);
+          }
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+          if (act[u]) {
+            if ((lane & 15) == 0) {
+              delta_sel[(size_t)hh[u] * cap + r] = acc;
+              lse_sel[(size_t)hh[u] * cap + r] = lv[u];
+            }
+            if (gathered) {
+              const size_t dst = ((size_t)r * hq + hh[u]) * HEAD_DIM + col;
+              *reinterpret_cast<uint4*>(q_sel + dst) = qv[u];
+              *reinterpret_cast<uint4*>(do_sel + dst) = dv[u];
+            }
+          }
         }
       }
     } else {
       // padding rows behind the last selected row: tiles may read them, keep them finite
-      for (int hh = 0; hh < hq; ++hh) {
-        const size_t dst = ((size_t)r * hq + hh) * HEAD_DIM + lane * 4;
-        *reinterpret_cast<uint2*>(q_sel + dst) = make_uint2(0, 0);
-        *reinterpret_cast<uint2*>(do_sel + dst) = make_uint2(0, 0);
-        if (lane == 0) {
-          delta_sel[(size_t)hh * cap + r] = 0.f;
-          lse_sel[(size_t)hh * cap + r] = 0.f;
+      for (int hb = 0; hb < hq; hb += 2) {
+        const int h1 = hb + sub;
+        if (h1 < hq) {
+          const size_t dst = ((size_t)r * hq + h1) * HEAD_DIM + col;
+          *reinterpret_cast<uint4*>(q_sel + dst) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(do_sel + dst) = make_uint4(0, 0, 0, 0);
+          if ((lane & 15) == 0) {
+            delta_sel[(size_t)h1 * cap + r] = 0.f;
+            lse_sel[(size_t)h1 * cap + r] = 0.f;
+          }
         }
       }
     }
@@ -245,7 +269,7 @@ __device__ __forceinline__ void dq_decode_item(const BwdArgs& a, int w, int tota
   }
 }
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                        const BwdArgs a) {
@@ -280,9 +304,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       mbar_init(&s_full[s], 1);
     }
     mbar_init(&dp_full, 1);
-    mbar_init(&ds_ready, 256);
+    mbar_init(&ds_ready, DQ_EW_WARPS * 32);
     mbar_init(&acc_done, 1);
-    ring_init(ring);
+    ring_init(ring, DQ_EW_WARPS + 1);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -298,11 +322,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const int total_tiles = __ldg(a.n_qtiles);
   const long long total_items = (long long)total_tiles * a.hq;
 
-  if (warp < 8) {
-    const int quad = warp & 3, half = warp >> 2;
+  if (warp < DQ_EW_WARPS) {
+    // Sixteen element-wise warps: warp w works on the 32 rows of lane quarter w % 4 and the 32 key
+    // columns [32 * (w / 4), +32). Four warps per scheduler keep its pipes fed while one of them waits
+    // on tensor memory or a barrier; with eight warps (64 columns each) the instruction stream of a
+    // warp was the bottleneck.
+    const int quad = warp & 3, part = warp >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const int col0 = half * 64;
+    const int col0 = part * 32;
     const float c = a.scale_log2;
     uint32_t idx = 0;      // key steps processed so far (all items)
     uint32_t n_items = 0;
@@ -327,28 +355,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const bool masked =
             (j * TILE + TILE - 1 > it.min_pos) || (a.window > 0 && j * TILE < it.max_pos - a.window);
         const uint32_t tS = TM_S + (idx & 1u) * 128u + lane_off + (uint32_t)col0;
-        uint32_t p0[32], p1[32];
+        uint32_t p0[32];
         mbar_wait(&s_full[idx & 1u], (idx >> 1) & 1u, ab);
         tc_fence_after();
         tmem_ld32(tS, p0);
-        tmem_ld32(tS + 32, p1);
         tmem_ld_wait();
         prob_chunk_row(p0, c, lse_r, masked, j * TILE + col0, key_hi, key_lo);
-        prob_chunk_row(p1, c, lse_r, masked, j * TILE + col0 + 32, key_hi, key_lo);
         mbar_wait(&dp_full, idx & 1u, ab);
         tc_fence_after();
-        uint32_t pk[32];
+        uint32_t pk[16];
         {
-          uint32_t d0[32], d1[32];
+          uint32_t d0[32];
           tmem_ld32(TM_DP + lane_off + (uint32_t)col0, d0);
-          tmem_ld32(TM_DP + lane_off + (uint32_t)col0 + 32, d1);
           tmem_ld_wait();
           ds_pack_chunk_row(p0, d0, delta_r, pk);
-          ds_pack_chunk_row(p1, d1, delta_r, pk + 16);
         }
-        // dS (bf16) goes into the first 32 of the 64 dP columns this warp has just read: no other warp
+        // dS (bf16) goes into the first 16 of the 32 dP columns this warp has just read: no other warp
         // reads or writes them, so no barrier is needed before the overwrite
-        tmem_st32(TM_DP + lane_off + (uint32_t)col0, pk);
+        tmem_st16(TM_DP + lane_off + (uint32_t)col0, pk);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&ds_ready);
@@ -363,20 +387,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tok = a.q_idx ? __ldg(a.q_idx + it.bos_q + it.r_base + row) : (long long)(it.bos_k + it.r_base + row);
       const bool store = tok >= 0 && tok < a.n_tokens;
       const long long row_off = store ? (long long)(((size_t)tok * a.hq + it.hq) * HEAD_DIM + col0) : -1;
-#pragma unroll
-      for (int chk = 0; chk < 2; ++chk) {
+      {
         uint32_t r[32], pk[16];
-        tmem_ld32(TM_DQ + lane_off + (uint32_t)col0 + chk * 32, r);
+        tmem_ld32(TM_DQ + lane_off + (uint32_t)col0, r);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * a.scale, __uint_as_float(r[2 * i + 1]) * a.scale);
-        store_patch_32x32(s_stage[warp], pk, a.dq, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+        // eight staging buffers for sixteen warps: two rounds
+        if (part < 2) store_patch_32x32(s_stage[warp], pk, a.dq, row_off, lane);
+        named_barrier_sync(1, DQ_EW_WARPS * 32);
+        if (part >= 2) store_patch_32x32(s_stage[warp - 8], pk, a.dq, row_off, lane);
       }
       tc_fence_before();
       ring_release(ring, n_ring);
     }
-  } else if (warp == 8) {
+  } else if (warp == DQ_EW_WARPS) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
@@ -443,8 +469,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                                      idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-        umma_tile_k128<true, true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
-                                         acc ? 1u : 0u);
+        umma_tile_k128<true, true, 4>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+                                      acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
@@ -600,7 +626,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     mbar_init(&p_ready, 256);
     mbar_init(&ds_ready, 256);
     mbar_init(&acc_done, 1);
-    ring_init(ring);
+    ring_init(ring, 9);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -865,7 +891,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                                      idesc_kk, 0u);
       };
       auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
-        umma_tile_k128<true, true, true>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+        umma_tile_k128<true, true, 2>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
                                          acc ? 1u : 0u);
       };
 
@@ -1044,7 +1070,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   prof_end(PROF_BWD_DKV, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_DQ, stream);
-  attn_bwd_dq_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  attn_bwd_dq_kernel<<<sms, DQ_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
   prof_end(PROF_BWD_DQ, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;

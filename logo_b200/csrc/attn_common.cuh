@@ -67,18 +67,17 @@ __device__ __forceinline__ int find_sequence(const int32_t* __restrict__ off, in
 // the loads it issues, so the MMA warp and the eight element-wise warps never wait for a decode.
 constexpr int ITEM_RING = 4;
 constexpr int ITEM_WORDS = 20;          // ints per published record; word 0 is the item index or -1
-constexpr int ITEM_CONSUMER_WARPS = 9;
 
 struct ItemRing {
   volatile int* items;   // [ITEM_RING][ITEM_WORDS]
   uint64_t* full;        // [ITEM_RING] count 1
-  uint64_t* empty;       // [ITEM_RING] count ITEM_CONSUMER_WARPS
+  uint64_t* empty;       // [ITEM_RING] count = number of consumer warps
 };
 
-__device__ __forceinline__ void ring_init(const ItemRing& r) {
+__device__ __forceinline__ void ring_init(const ItemRing& r, int consumer_warps) {
   for (int i = 0; i < ITEM_RING; ++i) {
     mbar_init(&r.full[i], 1);
-    mbar_init(&r.empty[i], ITEM_CONSUMER_WARPS);
+    mbar_init(&r.empty[i], consumer_warps);
   }
 }
 

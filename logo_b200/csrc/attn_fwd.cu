@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&p_ready[t], TILE);
       mbar_init(&o_done[t], 1);
     }
-    ring_init(ring);
+    ring_init(ring, 9);   // eight softmax warps + the MMA warp
     fence_barrier_init();
   }
   if (warp == 0) {

@@ -251,18 +251,20 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 //   A_TMEM: A comes from tensor memory (8 columns per k-step), else from K-major 128B-swizzled
 //           shared memory (two [128][64] blocks: 32 bytes per k-step, 16 KB between the blocks);
 //   B_MN  : B is MN-major ([k][n] rows as they lie in memory, 2 KB per k-step), else K-major.
-//   A_SPLIT (with A_TMEM): the second half of the k range (k-steps 4-7) starts 64 columns after the
-//           first instead of 32: each half of A then lies inside the 64 fp32 columns it was computed
-//           from, so the warps that produce the two halves never touch each other's columns.
-template <bool A_TMEM, bool B_MN, bool A_SPLIT = false>
+//   A_SPLIT (with A_TMEM): 0: A is 64 contiguous columns; 2: two halves of 32 columns, the second
+//           64 columns after the first; 4: four quarters of 16 columns, 32 columns apart. With 2 / 4
+//           every part of A lies inside the fp32 columns it was computed from, so the warps that
+//           produce the parts never touch each other's columns.
+//   K_BEGIN, K_END: the k-steps to issue (default all eight); `accumulate_first` applies to K_BEGIN.
+template <bool A_TMEM, bool B_MN, int A_SPLIT = 0, int K_BEGIN = 0, int K_END = 8>
 __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
                                                uint32_t accumulate_first) {
   if (elect_one()) {
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
+    for (int kk = K_BEGIN; kk < K_END; ++kk) {
       const uint32_t kmaj = (uint32_t)(kk >> 2) * 1024u + (uint32_t)(kk & 3) * 2u;   // K-major advance, 16 B units
       const uint64_t b = b0 + (B_MN ? (uint64_t)kk * 128u : (uint64_t)kmaj);
-      const uint32_t acc = kk > 0 ? 1u : accumulate_first;
+      const uint32_t acc = kk > K_BEGIN ? 1u : accumulate_first;
       if (A_TMEM) {
         asm volatile(
             "{\n\t"
@@ -271,7 +273,8 @@ __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uin
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
             "}\n"
             :
-            : "r"(d_tmem), "r"((uint32_t)a0 + (uint32_t)kk * 8u + ((A_SPLIT && kk >= 4) ? 32u : 0u)), "l"(b), "r"(idesc),
+            : "r"(d_tmem), "r"((uint32_t)a0 + (A_SPLIT == 4 ? (uint32_t)(kk >> 1) * 32u + (uint32_t)(kk & 1) * 8u
+                                                : (uint32_t)kk * 8u + ((A_SPLIT == 2 && kk >= 4) ? 32u : 0u))), "l"(b), "r"(idesc),
               "r"(acc)
             : "memory");
       } else {
