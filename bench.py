@@ -268,7 +268,10 @@ def run_gpu(args):
     dom_flops = 2.0 * f_fwd
     achieved = dom_flops / (kernel_ms[dom] * 1e-3) / 1e12 if kernel_ms[dom] else None
     roofline = {"bound": "tensor", "kernel": "attn_bwd_dkv_kernel", "achieved": achieved, "peak": peaks["bf16"],
-                "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None, "traffic": None,
+                "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this very
+                # workload at ratio 0.5 (ncu capture summarised under profiles/); other ratios: not captured
+                "traffic": 639.5e6 if abs(args.ratio - 0.5) < 1e-9 else None,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst"}
     kernel_tflops = {
         "attn_fwd": f_fwd / (kernel_ms["attn_fwd"] * 1e-3) / 1e12 if kernel_ms["attn_fwd"] else None,
