@@ -390,7 +390,18 @@ def run_decode(args):
     thres = torch.tensor([0.5], device=device)
     n_active = int((gate.float() >= 0.5).sum().item())
     bytes_step = (n_active * 2 * ctx + B * 2 * min(ctx, window + 1)) * heads * D * 2 + 4 * B * heads * D * 2
-    ms = _timed(lambda: decode_attention(ql, qg, st, gate, thres, SCALE), args.steps, args.warmup, dist, world)
+    from logo_b200 import ops
+    wl, wg = (mk(D) * 0.1 + 1), (mk(D) * 0.1 + 1)
+    slices = torch.empty(world, B, heads * D, dtype=torch.bfloat16, device=device) if world > 1 else None
+
+    def step():
+        local, glob = decode_attention(ql, qg, st, gate, thres, SCALE)
+        fused = ops.fuse_norm_blend(local, glob, gate, thres, wl, wg, 1e-5, True)     # [B, heads * D] of this rank's heads
+        if world > 1:   # every rank gets the attention output of all heads before the replicated o_proj
+            dist.all_gather_into_tensor(slices, fused)
+        return fused
+
+    ms = _timed(step, args.steps, args.warmup, dist, world)
     if rank == 0:
         gbs = bytes_step * world * args.steps / (ms * 1e-3) / 1e9
         print(json.dumps({
@@ -398,7 +409,8 @@ def run_decode(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"decode attention, one layer-step, B={B}, ctx={ctx}, {16} kv heads sharded over "
-                                   f"{world} rank(s), {n_active}/{B} sequences active", "bytes_per_step": bytes_step * world},
+                                   f"{world} rank(s), {n_active}/{B} sequences active; step = decode attention + norm/blend "
+                                   "(+ all-gather of the head slices when sharded)", "bytes_per_step": bytes_step * world},
             "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": gbs / world, "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": gbs / world / peaks["hbm"], "traffic": None,
                          "peak_source": f"{peaks['source']} copy bandwidth"}}))
@@ -459,6 +471,20 @@ def run_fuse(args):
         dist.destroy_process_group()
 
 
+def lpt_partition(lens, world, ratio, window=128):
+    """Whole sequences -> ranks, longest-processing-time first on the estimated attention cost
+    ratio * L^2 / 2 + (window + 1) * L (global causal rows + local window rows). Returns the list of
+    sequence indices of every rank; deterministic, so every rank computes the same plan."""
+    cost = [ratio * l * l / 2 + (window + 1) * l for l in lens]
+    order = sorted(range(len(lens)), key=lambda i: (-cost[i], i))
+    load, plan = [0.0] * world, [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda k: (load[k], k))
+        plan[r].append(i)
+        load[r] += cost[i]
+    return plan
+
+
 def _varlen_lengths(total, count, lo, hi, seed):
     rs = np.random.RandomState(seed)
     raw = rs.uniform(lo, hi, count)
@@ -476,7 +502,9 @@ def run_layer(args):
 
     dist, world, rank, device = _dist_setup()
     lens = sorted(_varlen_lengths(N_TOK, 8, 512, 8192, 5), reverse=True)
-    mine = [l for i, l in enumerate(lens) if i % world == rank] if world > 1 else lens
+    plan = lpt_partition(lens, world, 0.25)
+    mine = [lens[i] for i in plan[rank]]
+    n_max = max(sum(lens[i] for i in p_) for p_ in plan)      # rows every rank contributes to the gather
     cfg = LoGoConfig(hidden_size=2048, num_attention_heads=16, num_key_value_heads=16, window_size=128,
                      global_qk_param="linear_proj", num_hidden_layers=1, rms_norm_eps=1e-5,
                      max_position_embeddings=8192)
@@ -492,9 +520,15 @@ def run_layer(args):
         gate = torch.sigmoid(layer.gate_proj(hidden)).float().flatten()
         layer.gate_thres.fill_(torch.quantile(gate, 0.75).item())
 
+    gathered = torch.empty(world, n_max, 2048, dtype=torch.bfloat16, device=device) if world > 1 else None
+    mine_pad = torch.zeros(n_max, 2048, dtype=torch.bfloat16, device=device) if world > 1 else None
+
     def step():
         hidden.grad = None
         out, _, _ = layer(hidden, position_ids=pos, cu_seqlens=cu)
+        if world > 1:   # the one collective of the step: every rank ends up with all layer outputs
+            mine_pad[:n].copy_(out.detach()[0])
+            dist.all_gather_into_tensor(gathered, mine_pad)
         out.backward(d_out)
 
     ms = _timed(step, args.steps, args.warmup, dist, world)
@@ -505,7 +539,9 @@ def run_layer(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "LoGo attention layer fwd+bwd, 8 packed sequences (lengths " + str(lens) +
-                                   "), hidden 2048, 16x128, window 128, global ratio 0.25"}}))
+                                   "), hidden 2048, 16x128, window 128, global ratio 0.25; sequences dealt to the "
+                                   "ranks longest-cost-first, layer outputs all-gathered (NCCL) inside the step",
+                       "tokens_per_rank": [sum(lens[i] for i in p_) for p_ in plan]}}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -553,13 +589,19 @@ def run_prefill(args):
     ids = torch.randint(0, 32000, (b_local, t), device=device, generator=torch.Generator(device=device).manual_seed(rank))
     pos = torch.arange(t, device=device)[None].expand(b_local, -1)
 
+    logits_all = torch.empty(8, 32000, dtype=torch.bfloat16, device=device) if world > 1 else None
+
     @torch.no_grad()
     def step():
         x = emb(ids)
         pos_emb = blocks[0].attn.rotary_emb(x, pos)
         for blk in blocks:
             x = blk(x, pos_emb, pos)
-        return F.linear(norm_f(x[:, -1]), emb.weight)
+        logits = F.linear(norm_f(x[:, -1]), emb.weight)
+        if world > 1:   # last-token logits of the whole batch on every rank
+            dist.all_gather_into_tensor(logits_all, logits.contiguous())
+            return logits_all
+        return logits
 
     ms = _timed(step, args.steps, args.warmup, dist, world)
     if rank == 0:
@@ -569,7 +611,8 @@ def run_prefill(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "24-layer LoGo decoder stack prefill, 8 x 8192 tokens, hidden 2048, MLP 5632, "
-                                   "vocab 32000, gate threshold 0.5; attention layers from this package, the rest torch"}}))
+                                   "vocab 32000, gate threshold 0.5; attention layers from this package, the rest torch; "
+                                   "batch-sharded, last-token logits all-gathered (NCCL)"}}))
     if world > 1:
         dist.destroy_process_group()
 
