@@ -211,6 +211,17 @@ int logo_fuse_bwd(const void* d_out, const void* local, const void* glob, const 
                   int d, float eps, int use_norm, void* workspace, size_t workspace_bytes, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * RMSNorm forward over rows of any width (logo/modules/layernorm.py:9-26, the module the model
+ * also uses for its decoder-stack norms):
+ *     out = weight * bf16(x * rsqrt(mean(x^2) + eps))
+ *   x, out [rows, dim] bf16 contiguous, weight [dim] bf16, dim a multiple of 8.
+ * Inference path only (no gradient kernel): the Python module falls back to the eager expression
+ * whenever autograd needs the graph.
+ * ------------------------------------------------------------------------------------------ */
+int logo_rmsnorm_fwd(const void* x, const void* weight, void* out, long long rows, int dim, float eps,
+                     logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Rotary position embedding. Replaces apply_rotary_pos_emb (logo/modules/rotary.py:81-106, rotate_half :81-85) as
  * called at logo/layers/logo.py:136-139 for both branches:
  *     out = (x * cos) + (rotate_half(x) * sin)

@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
       mbar_init(&s_full[s], 1);
     }
     mbar_init(&dp_full, 1);
-    mbar_init(&ds_ready, DQ_EW_WARPS * 32);
+    mbar_init(&ds_ready, DQ_EW_WARPS);   // one arrival per warp
     mbar_init(&acc_done, 1);
     ring_init(ring, DQ_EW_WARPS + 1);
     fence_barrier_init();
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
         tmem_st16(TM_DP + lane_off + (uint32_t)col0, pk);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&ds_ready);
+        mbar_arrive_warp(&ds_ready);
       }
 
       // ---- epilogue: dQ * scale -> bf16 rows ----
@@ -623,8 +623,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
     mbar_init(&st_full, 1);
     mbar_init(&dpt_full, 1);
-    mbar_init(&p_ready, 256);
-    mbar_init(&ds_ready, 256);
+    mbar_init(&p_ready, 8);    // one arrival per warp
+    mbar_init(&ds_ready, 8);
     mbar_init(&acc_done, 1);
     ring_init(ring, 9);
     fence_barrier_init();
@@ -763,7 +763,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tmem_st32(TM_ST + lane_off + (uint32_t)col0, pk);
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(&p_ready);
+          mbar_arrive_warp(&p_ready);
         }
         mbar_wait(&dpt_full, idx & 1u, ab);
         tc_fence_after();
@@ -785,7 +785,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           tmem_st32(TM_DPT + lane_off + (uint32_t)col0, pk);
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(&ds_ready);
+          mbar_arrive_warp(&ds_ready);
         }
       }
 

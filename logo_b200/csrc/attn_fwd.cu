@@ -177,9 +177,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&v_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&q_ready[t], TILE);
+      mbar_init(&q_ready[t], TILE / 32);   // one arrival per warp
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_ready[t], TILE);
+      mbar_init(&p_ready[t], TILE / 32);
       mbar_init(&o_done[t], 1);
     }
     ring_init(ring, 9);   // eight softmax warps + the MMA warp
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       if (it.nrows[t] > 0) {
         gather_query_tile(a, it, t, row, sQt);
         tc_fence_before();
-        mbar_arrive(&q_ready[t]);
+        mbar_arrive_warp(&q_ready[t]);
       }
     }
     while (w >= 0) {
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           if (it_next.nrows[t] > 0) {
             gather_query_tile(a, it_next, t, row, sQt);
             tc_fence_before();
-            mbar_arrive(&q_ready[t]);
+            mbar_arrive_warp(&q_ready[t]);
           }
         }
         ring_release(ring, n_ring);
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         l_run += l0 + l1;
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&p_ready[t]);
+        mbar_arrive_warp(&p_ready[t]);
         ++n_steps;
       }
 
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         if (it_next.nrows[t] > 0) {
           gather_query_tile(a, it_next, t, row, sQt);
           tc_fence_before();
-          mbar_arrive(&q_ready[t]);
+          mbar_arrive_warp(&q_ready[t]);
         }
       }
 

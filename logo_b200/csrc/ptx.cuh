@@ -83,6 +83,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One arrival for the whole warp: every lane's preceding work is ordered before it by the warp
+// barrier. A barrier that 128-512 threads arrive on individually costs one shared-memory atomic per
+// thread on the hand-off path; with this form its count is the number of WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 // Per-CTA abort state, shared by all waits of a kernel.
 struct AbortState {
   volatile int* smem_abort;  // CTA-wide flag in shared memory

@@ -44,6 +44,11 @@ class RMSNorm(nn.Module):
         self.variance_epsilon = eps
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        # inference on bf16 CUDA tensors: one kernel with the same roundings as the expression below
+        if (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                and hidden_states.shape[-1] % 8 == 0
+                and not (torch.is_grad_enabled() and (hidden_states.requires_grad or self.weight.requires_grad))):
+            return ops.rmsnorm(hidden_states, self.weight, self.variance_epsilon)
         input_dtype = hidden_states.dtype
         hidden_states = hidden_states.to(torch.float32)
         variance = hidden_states.pow(2).mean(-1, keepdim=True)

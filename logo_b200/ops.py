@@ -322,6 +322,26 @@ def sdpa_causal_ref(q, k, v, scale=None, cu_seqlens=None):
 
 
 # ----------------------------------------------------------------------------------------
+# RMSNorm over rows of any width, inference only (logo/modules/layernorm.py:9-26)
+# ----------------------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``weight * bf16(x * rsqrt(mean(x^2) + eps))`` over the last dimension of a bf16 CUDA tensor."""
+    lib = _lib.load()
+    _require_cuda(x, weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("the RMSNorm kernel takes bf16 activations and a bf16 weight")
+    dim = x.shape[-1]
+    if weight.numel() != dim:
+        raise ValueError("rmsnorm: weight must have the size of the last dimension")
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    rc = lib.logo_rmsnorm_fwd(xc.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), xc.numel() // dim, dim,
+                              float(eps), _lib.current_stream_ptr(x.device))
+    _lib.check(rc, "logo_rmsnorm_fwd")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
 # rotary position embedding (logo/modules/rotary.py:81-106, used at logo/layers/logo.py:136-139)
 # ----------------------------------------------------------------------------------------
 def _rope_call(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool) -> torch.Tensor:

@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own code.
 
-Run once, in a container that has the reference checkout (``LOGO_REFERENCE`` or
-``/root/reference``); the resulting ``*.npz`` files are committed and are all the tests need.
+Run once, where a checkout of the reference is available (its path in ``LOGO_REFERENCE``); the
+resulting ``*.npz`` files are committed and are all the tests need.
 
-    python tests/golden/make_golden.py
+    LOGO_REFERENCE=<reference checkout> python tests/golden/make_golden.py [fixture ...]
 
 The reference is imported unmodified. Four shims make it runnable without a GPU and with the
 installed transformers 5.x (the reference pins < 4.52):
@@ -29,7 +29,9 @@ import torch
 import triton
 import triton.language as tl
 
-REF = os.environ.get("LOGO_REFERENCE", "/root/reference")
+REF = os.environ.get("LOGO_REFERENCE")
+if not REF or not Path(REF, "logo").is_dir():
+    raise SystemExit("set LOGO_REFERENCE to a checkout of the reference (the directory that contains logo/)")
 OUT = Path(__file__).resolve().parent
 sys.path.insert(0, REF)
 sys.path.insert(0, str(OUT))

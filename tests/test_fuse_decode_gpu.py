@@ -172,3 +172,42 @@ def test_decode_long_context_many_splits(cuda_device):
     assert orc.abs_err(ref_g, o_g.float().cpu()) <= 1e-2
     assert orc.abs_err(ref_l, o_l.float().cpu()) <= 1e-2
     assert torch.all(o_g[1] == 0)
+
+
+def test_rmsnorm_kernel_reproduces_reference_bf16_module(cuda_device, golden):
+    """The row-wise RMSNorm kernel against the reference module's bf16 output (head rows of 128) and,
+    for a decoder-width row, against the oracle's restatement of the module."""
+    from logo_b200 import ops
+
+    g = golden["misc"]
+    rs = np.random.RandomState(77)
+    n, h, d = 64, 2, 128
+    local = _bf(rs.standard_normal((n, h, d)))
+    _glob = rs.standard_normal((n, h, d))
+    _gate = rs.uniform(0, 1, (n, 1))
+    wl = _bf(1 + 0.1 * rs.standard_normal(d))
+    got = ops.rmsnorm(local.to(cuda_device), wl.to(cuda_device), 1e-5).float().cpu().numpy().reshape(n, -1)
+    ref = g["fuse/norm_local_bf16"]
+    ulp = np.maximum(np.abs(ref), 2.0 ** -126) * 2.0 ** -7
+    assert np.all(np.abs(got - ref) <= ulp) and np.mean(got != ref) < 0.01
+
+    x = _bf(rs.standard_normal((37, 2048)) * 3)
+    w = _bf(1 + 0.1 * rs.standard_normal(2048))
+    want = orc.rmsnorm_ref(x, w, 1e-5).float().numpy()
+    got = ops.rmsnorm(x.to(cuda_device), w.to(cuda_device), 1e-5).float().cpu().numpy()
+    ulp = np.maximum(np.abs(want), 2.0 ** -126) * 2.0 ** -7
+    assert np.all(np.abs(got - want) <= ulp) and np.mean(got != want) < 0.01
+
+
+def test_rmsnorm_module_uses_kernel_only_without_autograd(cuda_device):
+    from logo_b200.layers import RMSNorm
+
+    torch.manual_seed(3)
+    m = RMSNorm(256, 1e-5).to(cuda_device, torch.bfloat16)
+    x = torch.randn(5, 256, device=cuda_device).to(torch.bfloat16)
+    with torch.no_grad():
+        fast = m(x)
+    slow = m(x.clone().requires_grad_(True))     # eager path: autograd needs the graph
+    assert slow.requires_grad and not fast.requires_grad
+    ulp = slow.detach().float().abs().clamp_min(2.0 ** -126) * 2.0 ** -7
+    assert torch.all((fast.float() - slow.detach().float()).abs() <= ulp)
