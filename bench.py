@@ -401,7 +401,25 @@ def run_decode(args):
             dist.all_gather_into_tensor(slices, fused)
         return fused
 
-    ms = _timed(step, args.steps, args.warmup, dist, world)
+    # The layer-step is four small launches: replayed as one CUDA graph (what a decode loop does),
+    # falling back to plain launches if capture is not possible.
+    run, graphed = step, False
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run, graphed = graph.replay, True
+    except Exception as exc:   # noqa: BLE001 - any capture problem means: measure the plain launches
+        print(f"decode step not captured ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
+        torch.cuda.synchronize()
+    ms = _timed(run, args.steps, args.warmup, dist, world)
     if rank == 0:
         gbs = bytes_step * world * args.steps / (ms * 1e-3) / 1e9
         print(json.dumps({
@@ -410,7 +428,8 @@ def run_decode(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"decode attention, one layer-step, B={B}, ctx={ctx}, {16} kv heads sharded over "
                                    f"{world} rank(s), {n_active}/{B} sequences active; step = decode attention + norm/blend "
-                                   "(+ all-gather of the head slices when sharded)", "bytes_per_step": bytes_step * world},
+                                   "(+ all-gather of the head slices when sharded)", "bytes_per_step": bytes_step * world,
+                       "cuda_graph": graphed},
             "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": gbs / world, "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": gbs / world / peaks["hbm"], "traffic": None,
                          "peak_source": f"{peaks['source']} copy bandwidth"}}))
