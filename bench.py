@@ -394,16 +394,20 @@ def run_decode(args):
     wl, wg = (mk(D) * 0.1 + 1), (mk(D) * 0.1 + 1)
     slices = torch.empty(world, B, heads * D, dtype=torch.bfloat16, device=device) if world > 1 else None
 
-    def step():
-        local, glob = decode_attention(ql, qg, st, gate, thres, SCALE)
-        fused = ops.fuse_norm_blend(local, glob, gate, thres, wl, wg, 1e-5, True)     # [B, heads * D] of this rank's heads
-        if world > 1:   # every rank gets the attention output of all heads before the replicated o_proj
-            dist.all_gather_into_tensor(slices, fused)
-        return fused
+    fused_out = torch.empty(B, heads * D, dtype=torch.bfloat16, device=device)
 
-    # The layer-step is four small launches: replayed as one CUDA graph (what a decode loop does),
-    # falling back to plain launches if capture is not possible.
-    run, graphed = step, False
+    def step():     # this rank's heads: attention over the cache, then norm / blend
+        local, glob = decode_attention(ql, qg, st, gate, thres, SCALE)
+        fused_out.copy_(ops.fuse_norm_blend(local, glob, gate, thres, wl, wg, 1e-5, True))
+
+    def gather():   # every rank gets the attention output of all heads before the replicated o_proj
+        if world > 1:
+            dist.all_gather_into_tensor(slices, fused_out)
+
+    # The layer-step is a handful of small launches: replayed as one CUDA graph (what a decode loop
+    # does), falling back to plain launches if capture is not possible. The collective stays outside
+    # the graph (a captured NCCL call would tie the graph's lifetime to the process group's).
+    run, graphed = (lambda: (step(), gather())), False
     try:
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
@@ -415,7 +419,7 @@ def run_decode(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step()
-        run, graphed = graph.replay, True
+        run, graphed = (lambda: (graph.replay(), gather())), True
     except Exception as exc:   # noqa: BLE001 - any capture problem means: measure the plain launches
         print(f"decode step not captured ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
         torch.cuda.synchronize()
