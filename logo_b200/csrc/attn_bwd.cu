@@ -1004,8 +1004,11 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   LOGO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, LOGO_ERR_INVALID,
                "attention backward workspace must be 256-byte aligned");
 
-  if (gathered)
-    LOGO_CHECK_CUDA(cudaMemsetAsync(dq, 0, (size_t)n_tokens * hq * HEAD_DIM * sizeof(__nv_bfloat16), stream));
+  if (gathered) {   // dQ of unselected rows is zero; the selected rows are written by the dQ kernel
+    const int rc0 = launch_zero_unselected_rows(dq, q_idx, sq_ptr, n_tokens,
+                                                (size_t)hq * HEAD_DIM * sizeof(__nv_bfloat16), stream);
+    if (rc0) return rc0;
+  }
 
   const int sms = sm_count();
   prof_begin(PROF_BWD_PRE, stream);

@@ -542,8 +542,10 @@ extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, voi
   if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
   LOGO_REQUIRE(q_idx && pos_ids && cu_seqlens_q && cu_seqlens_k && tile_off && meta, LOGO_ERR_INVALID,
                "selection metadata pointers must not be NULL");
-  if (zero_fill)
-    LOGO_CHECK_CUDA(cudaMemsetAsync(o, 0, (size_t)n_tokens * hq * HEAD_DIM * sizeof(__nv_bfloat16), stream));
+  if (zero_fill) {   // only the rows the kernel will not write
+    rc = launch_zero_unselected_rows(o, q_idx, meta, n_tokens, (size_t)hq * HEAD_DIM * sizeof(__nv_bfloat16), stream);
+    if (rc) return rc;
+  }
   AttnArgs a{};
   a.q = (const __nv_bfloat16*)q;
   a.k = (const __nv_bfloat16*)k;

@@ -36,6 +36,13 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Zeroes the rows of a [n_tokens, row_bytes] tensor that are NOT listed in the ascending index list
+// q_idx[0 .. *sq_ptr): the gaps between consecutive selected tokens, before the first and after the
+// last. Replaces a memset of the whole tensor (whose selected rows are overwritten anyway).
+// row_bytes must be a multiple of 16 and `base` 16-byte aligned.
+int launch_zero_unselected_rows(void* base, const int64_t* q_idx, const int32_t* sq_ptr, int n_tokens,
+                                size_t row_bytes, cudaStream_t stream);
+
 // Per-kernel event timing (see logo_profile_enable): kernels report under these indices.
 enum ProfKind { PROF_SELECT = 0, PROF_ATTN_FWD = 1, PROF_BWD_PRE = 2, PROF_BWD_DKV = 3, PROF_BWD_DQ = 4, PROF_KINDS = 5 };
 bool prof_enabled();
