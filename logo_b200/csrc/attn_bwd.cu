@@ -60,24 +60,24 @@ __device__ __forceinline__ int bwd_row_position(const BwdArgs& a, int bos_q, int
 
 
 // r[i] <- bits of p = 2^(s*c - lse) for 32 scores of one row; keys outside [key_lo, key_hi] give 0.
-// MASKED is a template parameter so that the unmasked (by far most frequent) instance is branch-free.
-template <bool MASKED>
+// MASK is a template parameter so that the unmasked (by far most frequent) instance is branch-free:
+// 0 no mask, 1 causal only (one comparison per element), 2 causal + window.
+template <int MASK>
 __device__ __forceinline__ void prob_chunk_row_t(uint32_t (&r)[32], float c, float lse, int k0, int key_hi, int key_lo) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     float pv = fast_exp2(fmaf(__uint_as_float(r[i]), c, -lse));
-    if (MASKED) {
-      const int key = k0 + i;
-      pv = (key <= key_hi && key >= key_lo) ? pv : 0.f;
-    }
+    if (MASK == 1) pv = (k0 + i <= key_hi) ? pv : 0.f;
+    if (MASK == 2) pv = (k0 + i <= key_hi && k0 + i >= key_lo) ? pv : 0.f;
     r[i] = __float_as_uint(pv);
   }
 }
 
 __device__ __forceinline__ void prob_chunk_row(uint32_t (&r)[32], float c, float lse, bool masked, int k0, int key_hi,
                                                int key_lo) {
-  if (masked) prob_chunk_row_t<true>(r, c, lse, k0, key_hi, key_lo);
-  else prob_chunk_row_t<false>(r, c, lse, k0, key_hi, key_lo);
+  if (!masked) prob_chunk_row_t<0>(r, c, lse, k0, key_hi, key_lo);
+  else if (key_lo == INT32_MIN) prob_chunk_row_t<1>(r, c, lse, k0, key_hi, key_lo);
+  else prob_chunk_row_t<2>(r, c, lse, k0, key_hi, key_lo);
 }
 
 // pk[i] <- bf16x2 of p * (dp - delta) for 32 elements of one row
@@ -92,17 +92,17 @@ __device__ __forceinline__ void ds_pack_chunk_row(const uint32_t (&p)[32], const
 }
 
 // Column-wise variants for the transposed tiles of the dK/dV kernel: lse / delta / position differ per
-// column and come from shared memory (16-byte broadcast loads).
-template <bool MASKED>
+// column and come from shared memory (16-byte broadcast loads). MASK as above; an invalid key row
+// (past the end of the sequence) is passed as key_pos = INT32_MAX, which no query position reaches.
+template <int MASK>
 __device__ __forceinline__ void prob_chunk_col_t(uint32_t (&r)[32], float c, const float* __restrict__ lse_s,
-                                                 const int* __restrict__ pos_s, bool key_valid, int key_pos,
-                                                 int window) {
+                                                 const int* __restrict__ pos_s, int key_pos, int window) {
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
     const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 4 * g);
     const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
     int pv4[4] = {0, 0, 0, 0};
-    if (MASKED) {
+    if (MASK != 0) {
       const int4 q4 = *reinterpret_cast<const int4*>(pos_s + 4 * g);
       pv4[0] = q4.x;
       pv4[1] = q4.y;
@@ -112,11 +112,8 @@ __device__ __forceinline__ void prob_chunk_col_t(uint32_t (&r)[32], float c, con
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float pv = fast_exp2(fmaf(__uint_as_float(r[4 * g + e]), c, -lv[e]));
-      if (MASKED) {
-        const int qp = pv4[e];
-        const bool ok = key_valid && key_pos <= qp && (window == 0 || key_pos >= qp - window);
-        pv = ok ? pv : 0.f;
-      }
+      if (MASK == 1) pv = (key_pos <= pv4[e]) ? pv : 0.f;
+      if (MASK == 2) pv = (key_pos <= pv4[e] && key_pos >= pv4[e] - window) ? pv : 0.f;
       r[4 * g + e] = __float_as_uint(pv);
     }
   }
@@ -125,8 +122,10 @@ __device__ __forceinline__ void prob_chunk_col_t(uint32_t (&r)[32], float c, con
 __device__ __forceinline__ void prob_chunk_col(uint32_t (&r)[32], float c, const float* __restrict__ lse_s,
                                                const int* __restrict__ pos_s, bool masked, bool key_valid,
                                                int key_pos, int window) {
-  if (masked) prob_chunk_col_t<true>(r, c, lse_s, pos_s, key_valid, key_pos, window);
-  else prob_chunk_col_t<false>(r, c, lse_s, pos_s, key_valid, key_pos, window);
+  const int kp = key_valid ? key_pos : INT32_MAX;
+  if (!masked) prob_chunk_col_t<0>(r, c, lse_s, pos_s, kp, window);
+  else if (window == 0) prob_chunk_col_t<1>(r, c, lse_s, pos_s, kp, window);
+  else prob_chunk_col_t<2>(r, c, lse_s, pos_s, kp, window);
 }
 
 __device__ __forceinline__ void ds_pack_chunk_col(const uint32_t (&p)[32], const uint32_t (&dp)[32],
