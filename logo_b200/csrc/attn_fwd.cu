@@ -77,13 +77,20 @@ __device__ __forceinline__ bool tile_active(const FwdItem& it, int t, int j) {
   return it.nrows[t] > 0 && j >= it.jb[t] && j < it.je[t];
 }
 
-// keys outside [key_lo, key_hi] get a score of -inf
-__device__ __forceinline__ void mask_chunk(uint32_t (&r)[32], int k0, int key_hi, int key_lo) {
+// keys outside [key_lo, key_hi] get a score of -inf; WINDOWED = false: causal only, key_lo is ignored
+template <bool WINDOWED>
+__device__ __forceinline__ void mask_chunk_t(uint32_t (&r)[32], int k0, int key_hi, int key_lo) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const int key = k0 + i;
-    if (!(key <= key_hi && key >= key_lo)) r[i] = 0xff800000u;
+    const bool ok = WINDOWED ? (key <= key_hi && key >= key_lo) : (key <= key_hi);
+    if (!ok) r[i] = 0xff800000u;
   }
+}
+
+__device__ __forceinline__ void mask_chunk(uint32_t (&r)[32], int k0, int key_hi, int key_lo) {
+  if (key_lo == INT32_MIN) mask_chunk_t<false>(r, k0, key_hi, key_lo);
+  else mask_chunk_t<true>(r, k0, key_hi, key_lo);
 }
 
 __device__ __forceinline__ float max_chunk(const uint32_t (&r)[32]) {
