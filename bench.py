@@ -675,6 +675,102 @@ def run_prefill(args):
         dist.destroy_process_group()
 
 
+def run_decode_model(args):
+    """Decode step of the 24-layer, hidden-2048 stack (the 1.5B configuration): B sequences with a
+    32768-token cached context generate one token each. Attention layers (projections, rotary kernel,
+    in-place cache append, split-KV decode attention, norm/blend) are this package's; norms use the
+    row-wise RMSNorm kernel; the MLP is plain torch. The step is replayed as one CUDA graph.
+    B = 16 holds 103 GB of cache on one GPU (the 64-sequence configuration needs four GPUs)."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from logo_b200 import Cache, LoGoAttention
+    from logo_b200.config import LoGoConfig
+    from logo_b200.layers import RMSNorm
+
+    dist, world, rank, device = _dist_setup()
+    if world > 1:
+        raise SystemExit("decode_model measures the 1-GPU point; the sharded layer-step is --workload decode")
+    peaks = measured_peaks()
+    B, ctx, n_layers = args.decode_batch, 32768, 24
+    cfg = LoGoConfig(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=n_layers,
+                     num_attention_heads=16, num_key_value_heads=16, window_size=128, global_qk_param="linear_proj",
+                     gate_thres_init=0.5, rms_norm_eps=1e-5, max_position_embeddings=ctx + 64)
+
+    class Block(nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            self.ln1, self.ln2 = RMSNorm(2048, 1e-5), RMSNorm(2048, 1e-5)
+            self.attn = LoGoAttention(cfg, i)
+            self.gate_up = nn.Linear(2048, 2 * 5632, bias=False)
+            self.down = nn.Linear(5632, 2048, bias=False)
+
+        def forward(self, x, cache, pos):
+            x = x + self.attn(self.ln1(x), position_ids=pos, past_key_value=cache, use_cache=True)[0]
+            a, b = self.gate_up(self.ln2(x)).chunk(2, dim=-1)
+            return x + self.down(F.silu(a) * b)
+
+    torch.manual_seed(0)
+    blocks = nn.ModuleList([Block(i) for i in range(n_layers)])
+    for m in blocks.modules():
+        if isinstance(m, nn.Linear):
+            nn.init.normal_(m.weight, std=0.02)
+    blocks = blocks.to(device, torch.bfloat16).eval()
+    g = torch.Generator(device=device).manual_seed(7)
+    mk = lambda *sh: torch.randn(*sh, device=device, generator=g).to(torch.bfloat16)
+    cache = Cache(max_length=ctx + 32)
+    chunk = 4096
+    for layer in range(n_layers):      # synthetic context: fill every layer's cache in chunks
+        for _ in range(ctx // chunk):
+            cache.append(layer, mk(B, chunk, 16, D), mk(B, chunk, 16, D), mk(B, chunk, 16, D), mk(B, chunk, 16, D), 128)
+    x = mk(B, 1, 2048)
+    out = torch.empty_like(x)
+
+    @torch.no_grad()
+    def step():
+        # every eager call appends one token; the captured graph re-writes the slot it was captured at
+        pos = torch.full((B, 1), cache.layers[0].length, dtype=torch.long, device=device)
+        h = x
+        for blk in blocks:
+            h = blk(h, cache, pos)
+        out.copy_(h)
+
+    run, graphed = step, False
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run, graphed = graph.replay, True
+    except Exception as exc:   # noqa: BLE001 - any capture problem means: measure the plain launches
+        print(f"decode step not captured ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
+        torch.cuda.synchronize()
+    ms = _timed(run, args.steps, args.warmup, dist, world)
+    with torch.no_grad():
+        gate = torch.sigmoid(blocks[0].attn.gate_proj(blocks[0].ln1(x))).float().flatten()
+    n_active = int((gate >= 0.5).sum().item())
+    t_step = ms / args.steps * 1e-3
+    n_param = sum(p.numel() for p in blocks.parameters())
+    cache_bytes = n_layers * (0.5 * B * 2 * ctx + B * 2 * 129) * 16 * D * 2     # half the sequences active per layer
+    print(json.dumps({
+        "metric": "logo_1b5_decode_tokens_per_s", "value": B / t_step, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"24-layer LoGo decoder stack, one decode step, B={B}, cached context {ctx}, "
+                               "gate threshold 0.5 (about half the sequences take the global branch per layer); "
+                               "no embedding / lm_head", "cuda_graph": graphed, "active_in_layer_0": n_active},
+        "roofline": {"bound": "hbm", "achieved": (cache_bytes + 2 * n_param) / t_step / 1e9, "peak": peaks["hbm"],
+                     "unit": "GB/s", "frac": (cache_bytes + 2 * n_param) / t_step / 1e9 / peaks["hbm"], "traffic": None,
+                     "note": "expected bytes: K/V of the active sequences + local rings + every weight once",
+                     "peak_source": f"{peaks['source']} copy bandwidth"}}))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -701,7 +797,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ratio", type=float, default=0.5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "fuse", "layer", "prefill"],
+    ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "decode_model", "fuse", "layer", "prefill"],
                     help="sq_attn is the headline metric; the others measure further rows of the same path")
     ap.add_argument("--decode-batch", type=int, default=16)
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
@@ -714,7 +810,8 @@ def main():
     elif args.workload == "sq_attn":
         run_gpu(args)
     else:
-        {"decode": run_decode, "fuse": run_fuse, "layer": run_layer, "prefill": run_prefill}[args.workload](args)
+        {"decode": run_decode, "decode_model": run_decode_model, "fuse": run_fuse, "layer": run_layer,
+         "prefill": run_prefill}[args.workload](args)
 
 
 if __name__ == "__main__":
