@@ -43,6 +43,8 @@ GLOBAL_CASES = {
     "gqa4": ([400, 90], 4, 1, 0.6),
     "sparse_long": ([4096], 2, 1, 0.125),
     "single_token_seqs": ([1, 1, 1, 257], 2, 2, 1.0),
+    # more work items than SMs in every kernel: CTAs claim several items, the record ring wraps
+    "many_items": ([3000, 500], 16, 4, 0.8),
 }
 
 
@@ -90,6 +92,7 @@ LOCAL_CASES = {
     "varlen_gqa": ([70, 0, 130, 513, 1, 700], 4, 2, 128),
     "window64": ([1000], 2, 2, 64),
     "window200": ([900, 300], 2, 1, 200),
+    "many_items": ([2500, 700], 16, 16, 128),
 }
 
 
