@@ -41,6 +41,7 @@ GLOBAL_CASES = {
     "half_selected": ([1000], 2, 2, 0.5),
     "varlen_gqa_empty_seq": ([70, 0, 130, 513, 1, 700], 4, 2, 0.3),
     "gqa4": ([400, 90], 4, 1, 0.6),
+    "heads32_kv8": ([300, 140], 32, 8, 0.5),
     "sparse_long": ([4096], 2, 1, 0.125),
     "single_token_seqs": ([1, 1, 1, 257], 2, 2, 1.0),
     # more work items than SMs in every kernel: CTAs claim several items, the record ring wraps
