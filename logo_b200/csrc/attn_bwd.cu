@@ -4,17 +4,19 @@
 //   1. bwd_preprocess_kernel: delta = sum_d o * dO per (row, head); for the query-sparse
 //      branch it also packs the selected rows of Q and dO into contiguous buffers so the
 //      two GEMM kernels can stream them with TMA, and transposes lse to head-major.
-//   2. attn_bwd_dq_kernel: one CTA per (128-row query tile, head); streams K/V tiles.
+//   2. attn_bwd_dq_kernel: work item = (128-row query tile, head); streams K/V tiles.
 //        S = Q K^T, dP = dO V^T, dS = P o (dP - delta), dQ += dS K
-//   3. attn_bwd_dkv_kernel: one CTA per (128-key tile, kv head); streams Q/dO tiles of every
+//   3. attn_bwd_dkv_kernel: work item = (128-key tile, kv head); streams Q/dO tiles of every
 //      query head of the group (the GQA reduction happens in the accumulators).
 //        S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q
-// In both GEMM kernels warps 0-7 do the element-wise work: warp w owns TMEM lanes
-// 32*(w%4).. and the 64 columns starting at 64*(w/4) of each 128x128 tile; warp 8 is the
-// TMA producer and warp 9 issues the MMAs. P / dS are written back to tensor memory as
-// bf16 over the S / dP accumulators and consumed as the A operand of the next product;
-// the tile that supplies the B operand of that product ([rows][128] as it lies in memory)
-// is read through an MN-major descriptor.
+// Both GEMM kernels are persistent (one CTA per SM claims items from a global counter through
+// the record ring of attn_common.cuh). The element-wise warps split a 128x128 tile by TMEM lane
+// quarter (w % 4) and column range: eight warps x 64 columns in the dK/dV kernel, sixteen warps
+// x 32 columns in the dQ kernel; one further warp is the TMA producer and one issues the MMAs.
+// P / dS are written back to tensor memory as bf16 INSIDE the columns their warp read (so no
+// warp touches another warp's columns) and consumed as the A operand of the next product; the
+// tile that supplies the B operand of that product ([rows][128] as it lies in memory) is read
+// through an MN-major descriptor.
 //
 // Algorithmic work: 2.5x the forward FLOPs (5 products against 2); S is recomputed in both
 // GEMM kernels, so 7 products execute.

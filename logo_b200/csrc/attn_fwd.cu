@@ -4,11 +4,12 @@
 //                  computed; K/V of every token of the sequence stay visible;
 //   local branch : every row, keys [pos - window, pos].
 //
-// One CTA works on a pair of query tiles (2 x 128 compacted rows of one sequence and one
-// head). Ten warps:
+// A work item is a pair of query tiles (2 x 128 compacted rows of one sequence and one head);
+// the kernel is persistent (one CTA per SM claims items from a global counter through the record
+// ring of attn_common.cuh). Ten warps:
 //   warps 0-3 / 4-7 : softmax groups for query tile 0 / 1 (one thread per row)
-//   warp 8          : TMA producer, streams 128-key K and V tiles through 2-stage rings
-//   warp 9          : issues tcgen05.mma (one lane)
+//   warp 8          : claims / decodes items, TMA producer of the 128-key K and V tiles (2-stage rings)
+//   warp 9          : issues tcgen05.mma (whole warp walks the loop, an elected lane issues)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each. The bf16
 // probabilities overwrite the first 64 columns of their S buffer and are the A operand of
 // the P*V product straight from tensor memory; V is consumed as an MN-major B operand so
