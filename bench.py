@@ -97,6 +97,7 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
         self._stop_evt = threading.Event()
+        self.recording = False   # the thread starts before the warm-up (its first NVML calls are slow); samples count from begin()
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -111,18 +112,24 @@ class ClockSampler(threading.Thread):
             return
         while not self._stop_evt.is_set():
             try:
-                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                mhz = self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
                 get = getattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
                     self.nv.nvmlDeviceGetCurrentClocksThrottleReasons
                 mask = get(self.handle)
-                for bit, name in self.REASONS.items():
-                    if mask & bit and name != "gpu_idle":
-                        self.reasons.add(name)
+                if self.recording:
+                    self.samples.append(mhz)
+                    for bit, name in self.REASONS.items():
+                        if mask & bit and name != "gpu_idle":
+                            self.reasons.add(name)
             except Exception:
                 pass
-            self._stop_evt.wait(0.001)
+            self._stop_evt.wait(0.002)
+
+    def begin(self):
+        self.recording = True
 
     def finish(self):
+        self.recording = False
         self._stop_evt.set()
         self.join(timeout=2)
         med = float(np.median(self.samples)) if self.samples else None
@@ -184,17 +191,24 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     # ---- value: inputs resident in HBM ----
+    # Every event the timed region uses exists before it starts (the step marks are recorded once,
+    # the library's per-kernel events are reserved): creating CUDA events inside a timed loop can
+    # stall the stream for milliseconds when the driver grows its event pool.
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for ev in [e0, e1] + marks:
+        ev.record()
+    _lib.check(lib.logo_profile_reserve(8 * (args.steps + args.warmup)), "logo_profile_reserve")
+    lib.logo_profile_enable(1)
     for _ in range(args.warmup):
         m, *_ = device_step(batch)
     torch.cuda.synchronize()
     ops.check_device_status(m.status, "warm-up")
     lib.logo_profile_read(None, None, 0)
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    lib.logo_profile_enable(1)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sampler.begin()
     e0.record()
     for i in range(args.steps):
         m, *_ = device_step(batch)
@@ -346,7 +360,7 @@ def run_gpu(args):
         "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "step_ms_rank0": {"median": float(np.median(per_step)), "min": float(np.min(per_step)),
-                          "max": float(np.max(per_step))},
+                          "max": float(np.max(per_step)), "argmax": int(np.argmax(per_step))},
         "config": {"workload": "sq_full_attn fwd+bwd, 4x8192 tokens packed [1,32768,16,128], causal, "
                                f"Bernoulli({args.ratio}) row mask", "ratio": args.ratio,
                    "l2": "inputs (671 MB per step) exceed the 126 MB L2; no flush needed",

@@ -278,6 +278,9 @@ int logo_decode_attn(const void* q_local, const void* q_global, const void* k_ri
  *        3 backward dK/dV, 4 backward dQ
  * ------------------------------------------------------------------------------------------ */
 int logo_profile_enable(int on);
+/* Creates the events for `n_launches` timed kernel launches ahead of time (at most 4096), so that a
+ * timed loop creates none: the driver can stall a stream for milliseconds when its event pool grows. */
+int logo_profile_reserve(int n_launches);
 int logo_profile_read(double* total_ms, int* launches, int n);
 
 /* ------------------------------------------------------------------------------------------

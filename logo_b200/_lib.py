@@ -58,6 +58,7 @@ _SIGNATURES = {
                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
     "logo_profile_enable": (c_int, [c_int]),
+    "logo_profile_reserve": (c_int, [c_int]),
     "logo_profile_read": (c_int, [c_void_p, c_void_p, c_int]),
     "logo_umma_selftest": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
                                    c_void_p, c_void_p]),

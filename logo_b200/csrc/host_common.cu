@@ -72,13 +72,21 @@ struct ProfSlot {
 };
 static thread_local bool g_prof_on = false;
 static thread_local std::vector<ProfSlot>* g_prof = nullptr;   // [PROF_KINDS] vectors
+// Events are recycled: creating events in the middle of a timed loop can stall the stream for
+// milliseconds when the driver has to grow its event pool.
+static thread_local std::vector<ProfSlot>* g_prof_free = nullptr;
 
 bool prof_enabled() { return g_prof_on; }
 
 void prof_begin(int kind, cudaStream_t stream) {
   if (!g_prof_on || kind < 0 || kind >= PROF_KINDS) return;
   ProfSlot s{};
-  if (cudaEventCreate(&s.start) != cudaSuccess || cudaEventCreate(&s.stop) != cudaSuccess) return;
+  if (g_prof_free && !g_prof_free->empty()) {
+    s = g_prof_free->back();
+    g_prof_free->pop_back();
+  } else if (cudaEventCreate(&s.start) != cudaSuccess || cudaEventCreate(&s.stop) != cudaSuccess) {
+    return;
+  }
   cudaEventRecord(s.start, stream);
   g_prof[kind].push_back(s);
 }
@@ -93,7 +101,20 @@ void prof_end(int kind, cudaStream_t stream) {
 extern "C" int logo_profile_enable(int on) {
   using namespace logo;
   if (!g_prof) g_prof = new std::vector<ProfSlot>[PROF_KINDS];
+  if (!g_prof_free) g_prof_free = new std::vector<ProfSlot>();
   g_prof_on = (on != 0);
+  return LOGO_OK;
+}
+
+extern "C" int logo_profile_reserve(int n_launches) {
+  using namespace logo;
+  if (!g_prof_free) g_prof_free = new std::vector<ProfSlot>();
+  while ((int)g_prof_free->size() < n_launches && g_prof_free->size() < 4096) {
+    ProfSlot s{};
+    LOGO_CHECK_CUDA(cudaEventCreate(&s.start));
+    LOGO_CHECK_CUDA(cudaEventCreate(&s.stop));
+    g_prof_free->push_back(s);
+  }
   return LOGO_OK;
 }
 
@@ -109,8 +130,12 @@ extern "C" int logo_profile_read(double* total_ms, int* launches, int n) {
           total += ms;
           ++count;
         }
-        cudaEventDestroy(s.start);
-        cudaEventDestroy(s.stop);
+        if (g_prof_free && g_prof_free->size() < 4096) {
+          g_prof_free->push_back(s);
+        } else {
+          cudaEventDestroy(s.start);
+          cudaEventDestroy(s.stop);
+        }
       }
       g_prof[k].clear();
     }
