@@ -628,13 +628,13 @@ def run_layer(args):
 
 def run_prefill(args):
     """Prefill of a 24-layer, hidden-2048 LoGo decoder stack (the 1.5B configuration with vocabulary
-    32000): the attention layers are this package's, the rest (embedding, RMSNorm, SwiGLU MLP 5632,
-    lm_head on the last token) is plain torch. B = 8 x 8192 tokens, batch-sharded over the ranks,
+    32000): the attention layers, the RMSNorm and the gated activation of the MLP are this package's
+    kernels, the rest (embedding, MLP projections, residuals, lm_head on the last token) is plain torch. B = 8 x 8192 tokens, batch-sharded over the ranks,
     gate threshold 0.5. Random bf16 weights."""
     import torch.nn as nn
     import torch.nn.functional as F
 
-    from logo_b200 import LoGoAttention
+    from logo_b200 import LoGoAttention, ops
     from logo_b200.config import LoGoConfig
     from logo_b200.layers import RMSNorm
 
@@ -655,7 +655,7 @@ def run_prefill(args):
             x = x + self.attn(self.ln1(x), position_ids=pos, position_embeddings=pos_emb)[0]
             gu = self.gate_up(self.ln2(x))
             a, b = gu.chunk(2, dim=-1)
-            return x + self.down(F.silu(a) * b)
+            return x + self.down(ops.silu_mul(a, b))
 
     torch.manual_seed(0)
     emb = nn.Embedding(32000, 2048)
@@ -706,7 +706,7 @@ def run_decode_model(args):
     import torch.nn as nn
     import torch.nn.functional as F
 
-    from logo_b200 import Cache, LoGoAttention
+    from logo_b200 import Cache, LoGoAttention, ops
     from logo_b200.config import LoGoConfig
     from logo_b200.layers import RMSNorm
 
@@ -730,7 +730,7 @@ def run_decode_model(args):
         def forward(self, x, cache, pos):
             x = x + self.attn(self.ln1(x), position_ids=pos, past_key_value=cache, use_cache=True)[0]
             a, b = self.gate_up(self.ln2(x)).chunk(2, dim=-1)
-            return x + self.down(F.silu(a) * b)
+            return x + self.down(ops.silu_mul(a, b))
 
     torch.manual_seed(0)
     blocks = nn.ModuleList([Block(i) for i in range(n_layers)])

@@ -222,6 +222,16 @@ int logo_rmsnorm_fwd(const void* x, const void* weight, void* out, long long row
                      logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Gated activation of the model's MLP (logo/modules/mlp.py:25, hidden_act "silu"):
+ *     out = silu(gate) * up      (silu in fp32, rounded to bf16, then one bf16 multiplication)
+ *   gate, up: bf16 rows of `dim` elements at element strides gate_stride / up_stride (multiples of 8:
+ *   the two halves of a fused gate-up projection can be passed as views); out [rows, dim] packed.
+ * Inference path only (no gradient kernel).
+ * ------------------------------------------------------------------------------------------ */
+int logo_silu_mul(const void* gate, long long gate_stride, const void* up, long long up_stride, void* out,
+                  long long rows, int dim, logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Rotary position embedding. Replaces apply_rotary_pos_emb (logo/modules/rotary.py:81-106, rotate_half :81-85) as
  * called at logo/layers/logo.py:136-139 for both branches:
  *     out = (x * cos) + (rotate_half(x) * sin)

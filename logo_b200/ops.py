@@ -342,6 +342,29 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------------------
+# gated MLP activation, inference only (logo/modules/mlp.py:25)
+# ----------------------------------------------------------------------------------------
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` over bf16 CUDA tensors of equal shape whose last dimension is contiguous
+    (row-strided views, e.g. the two halves of a fused projection, are read in place)."""
+    lib = _lib.load()
+    _require_cuda(gate, up)
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape:
+        raise TypeError("silu_mul takes two bf16 tensors of the same shape")
+    dim = gate.shape[-1]
+    g2, u2 = gate.reshape(-1, dim), up.reshape(-1, dim)     # views when only the row stride is non-trivial
+    if g2.stride(1) != 1 or g2.stride(0) % 8 or g2.data_ptr() % 16:
+        g2 = g2.contiguous()
+    if u2.stride(1) != 1 or u2.stride(0) % 8 or u2.data_ptr() % 16:
+        u2 = u2.contiguous()
+    out = torch.empty(gate.shape, dtype=torch.bfloat16, device=gate.device)
+    rc = lib.logo_silu_mul(g2.data_ptr(), g2.stride(0), u2.data_ptr(), u2.stride(0), out.data_ptr(), g2.shape[0], dim,
+                           _lib.current_stream_ptr(gate.device))
+    _lib.check(rc, "logo_silu_mul")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
 # rotary position embedding (logo/modules/rotary.py:81-106, used at logo/layers/logo.py:136-139)
 # ----------------------------------------------------------------------------------------
 def _rope_call(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool) -> torch.Tensor:

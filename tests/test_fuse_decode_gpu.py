@@ -211,3 +211,21 @@ def test_rmsnorm_module_uses_kernel_only_without_autograd(cuda_device):
     assert slow.requires_grad and not fast.requires_grad
     ulp = slow.detach().float().abs().clamp_min(2.0 ** -126) * 2.0 ** -7
     assert torch.all((fast.float() - slow.detach().float()).abs() <= ulp)
+
+
+def test_silu_mul_matches_eager_bf16(cuda_device):
+    """silu(gate) * up on the two halves of a fused projection (row-strided views), against the eager
+    bf16 expression evaluated on the CPU (torch rounds silu to bf16, then multiplies in bf16)."""
+    from logo_b200 import ops
+
+    torch.manual_seed(4)
+    gu = (torch.randn(37, 2 * 5632) * 2).to(torch.bfloat16)
+    a, b = gu.chunk(2, dim=-1)
+    want = (torch.nn.functional.silu(a) * b).float()
+    gud = gu.to(cuda_device)
+    ad, bd = gud.chunk(2, dim=-1)
+    got = ops.silu_mul(ad, bd).float().cpu()
+    ulp = want.abs().clamp_min(2.0 ** -126) * 2.0 ** -7
+    assert torch.all((got - want).abs() <= ulp)       # expf differs in its last bits between CPU and GPU
+    assert (got != want).float().mean().item() < 0.01
+    assert ops.silu_mul(ad[:0], bd[:0]).shape == (0, 5632)
