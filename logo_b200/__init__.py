@@ -4,6 +4,7 @@ Public surface, mirroring the reference package ``logo``:
 
 * ``logo_b200.ops``      -- ``sq_full_attn``, ``build_selection``, ``SelInfo`` ... (``logo.ops``)
 * ``LoGoAttention``      -- the attention layer (``logo.layers.LoGoAttention``)
+* ``Attention``          -- the dense causal layer for non-LoGo layers (``logo.layers.attn.Attention``)
 * ``Cache``              -- the dual-state KV cache (``logo.cache.Cache``)
 * ``update_gate_thres``  -- the budget controller (``logo.update.update_gate_thres``)
 
@@ -12,9 +13,9 @@ no Triton, flash-attn or CPU path.
 """
 from . import ops
 from .cache import Cache
-from .layers import LoGoAttention
+from .layers import Attention, LoGoAttention
 from .ops import SelInfo, build_selection, sq_full_attn
 from .update import update_gate_thres
 
-__all__ = ["ops", "Cache", "LoGoAttention", "SelInfo", "build_selection", "sq_full_attn", "update_gate_thres"]
+__all__ = ["ops", "Attention", "Cache", "LoGoAttention", "SelInfo", "build_selection", "sq_full_attn", "update_gate_thres"]
 __version__ = "0.1.0"

@@ -28,7 +28,7 @@ import torch.nn as nn
 from . import _lib, ops
 from .cache import Cache
 
-__all__ = ["LoGoAttention", "RMSNorm", "RotaryEmbedding", "apply_rotary_pos_emb", "rotate_half"]
+__all__ = ["Attention", "LoGoAttention", "RMSNorm", "RotaryEmbedding", "apply_rotary_pos_emb", "rotate_half"]
 
 
 class RMSNorm(nn.Module):
@@ -320,3 +320,111 @@ def decode_attention(q_local, q_global, st, gate_flat, thres, scale: float):
                               _lib.current_stream_ptr(dev))
     _lib.check(rc, "logo_decode_attn")
     return o_local, o_global
+
+
+class Attention(nn.Module):
+    """Dense causal attention layer (drop-in for ``logo.layers.attn.Attention``, logo/layers/attn.py:22-121).
+
+    Used for layers whose ``attn_type_list`` entry is non-zero. It runs on the same kernels as the LoGo
+    layer: rotary kernel, then full causal attention as the all-rows path of the attention kernels with
+    a window that covers any sequence; a one-token step attends over the in-place cache with the decode
+    kernel (every sequence active).
+    """
+
+    _FULL_WINDOW = 1 << 30
+
+    def __init__(self, config, layer_idx: Optional[int] = None):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.hidden_size = config.hidden_size
+        self.num_heads = config.num_attention_heads
+        self.head_dim = self.hidden_size // self.num_heads
+        self.num_key_value_heads = config.num_key_value_heads
+        self.num_key_value_groups = self.num_heads // self.num_key_value_heads
+        self.max_position_embeddings = config.max_position_embeddings
+        self.rope_theta = config.rope_theta
+        self.is_causal = True
+        self.attention_dropout = config.attention_dropout
+        if (self.head_dim * self.num_heads) != self.hidden_size:
+            raise ValueError(
+                f"hidden_size must be divisible by num_heads (got `hidden_size`: {self.hidden_size}"
+                f" and `num_heads`: {self.num_heads})."
+            )
+        if self.head_dim != ops.HEAD_DIM:
+            raise NotImplementedError(f"the CUDA kernels implement head_dim {ops.HEAD_DIM} only, got {self.head_dim}")
+        if self.attention_dropout != 0.0:
+            raise NotImplementedError("attention dropout is not implemented")
+        self.q_proj = nn.Linear(self.hidden_size, self.num_heads * self.head_dim, bias=config.attention_bias)
+        self.k_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=config.attention_bias)
+        self.v_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=config.attention_bias)
+        self.o_proj = nn.Linear(self.hidden_size, self.hidden_size, bias=config.attention_out_bias)
+        self.resid_dropout = nn.Dropout(config.resid_pdrop)
+        self.rotary_emb = RotaryEmbedding(config=config)
+
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        attention_mask: Optional[torch.Tensor] = None,
+        position_ids: Optional[torch.LongTensor] = None,
+        cu_seqlens: Optional[torch.IntTensor] = None,
+        past_key_value=None,
+        output_attentions: bool = False,
+        use_cache: bool = False,
+        cache_position: Optional[torch.LongTensor] = None,
+        position_embeddings: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+        max_seqlen: Optional[int] = None,
+        **kwargs,
+    ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[object]]:
+        if not hidden_states.is_cuda:
+            raise RuntimeError("logo_b200.Attention runs on CUDA only; there is no CPU fallback")
+        bsz, q_len, _ = hidden_states.size()
+        H, HKV, D = self.num_heads, self.num_key_value_heads, self.head_dim
+        query_states = self.q_proj(hidden_states)
+        key_states = self.k_proj(hidden_states)
+        value_states = self.v_proj(hidden_states)
+        if query_states.dtype != torch.bfloat16:
+            raise TypeError("logo_b200.Attention needs bf16 activations (cast the model or use autocast)")
+        v = value_states.view(bsz, q_len, HKV, D)
+        if position_embeddings is None:
+            cos, sin = self.rotary_emb(v, position_ids)
+        else:
+            cos, sin = position_embeddings
+        n_tok = bsz * q_len
+        cos2 = cos.reshape(n_tok, D).to(torch.bfloat16)
+        sin2 = sin.reshape(n_tok, D).to(torch.bfloat16)
+        q = ops.rope(query_states.view(n_tok, H, D), cos2, sin2)          # [N, H, D]
+        k = ops.rope(key_states.view(n_tok, HKV, D), cos2, sin2)
+        scale = D ** -0.5
+
+        if past_key_value is not None and q_len == 1:
+            if not isinstance(past_key_value, Cache):
+                raise TypeError("decode needs a logo_b200.Cache")
+            kb, vb = k.view(bsz, 1, HKV, D), v
+            # the decode kernel serves both LoGo branches: give it a one-entry local ring and use its
+            # global output with every sequence active
+            st = past_key_value.append(self.layer_idx, kb, vb, kb, vb, 0, layout="bthd")
+            ones = torch.ones(bsz, dtype=torch.bfloat16, device=q.device)
+            zero = torch.zeros(1, dtype=torch.float32, device=q.device)
+            qd = q.view(bsz, H, D)
+            _, out = decode_attention(qd, qd, st, ones, zero, scale)
+            out = out.view(bsz, 1, H * D)
+        else:
+            if past_key_value is not None:
+                if not isinstance(past_key_value, Cache):
+                    raise TypeError("the cache must be a logo_b200.Cache")
+                filled = (past_key_value.layers[self.layer_idx].length
+                          if len(past_key_value.layers) > self.layer_idx else 0)
+                if filled != 0:
+                    raise NotImplementedError("multi-token steps on a non-empty cache are not implemented")
+                kb = k.view(bsz, q_len, HKV, D)
+                past_key_value.append(self.layer_idx, kb, v, kb, v, 0, layout="bthd")
+            if cu_seqlens is not None:
+                cu = cu_seqlens
+            else:
+                cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
+            out = ops.swa_attn(q, k, v.reshape(n_tok, HKV, D), cu, self._FULL_WINDOW, scale).view(bsz, q_len, H * D)
+
+        attn_output = self.o_proj(out)
+        attn_output = self.resid_dropout(attn_output)
+        return attn_output, None, past_key_value

@@ -164,3 +164,61 @@ def test_backend_string_and_dtype_errors(cuda_device):
         build_layer(case, cuda_device, dtype=torch.float32)(h.float(), position_ids=p)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         build_layer(case, "cpu")(h.cpu(), position_ids=p.cpu())
+
+
+def test_dense_attention_layer_vs_oracle(cuda_device):
+    """The dense causal layer (logo/layers/attn.py): forward against the fp32 oracle (projections, rotary
+    embedding, causal attention with every row selected), and one-token steps over the cache against the
+    rows of a longer forward."""
+    from logo_b200 import Attention, Cache
+    from logo_b200.config import LoGoConfig
+
+    cfg = LoGoConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=1,
+                     max_position_embeddings=4096)
+    torch.manual_seed(11)
+    layer = Attention(cfg, layer_idx=0)
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.normal_(0, 0.05)
+    # the oracle sees the bf16-rounded weights and inputs the layer computes with; what is left is the
+    # rounding inside the bf16 graph (q / k / v, P, the attention output), largest at the first
+    # positions where an output row is one value row rather than an average
+    w = {k: v.detach().clone().to(torch.bfloat16).float() for k, v in layer.named_parameters()}
+    layer = layer.to(cuda_device, torch.bfloat16).eval()
+    B, T, steps = 2, 300, 3
+    hidden = torch.randn(B, T + steps, 512).to(torch.bfloat16).float()
+    pos = torch.arange(T + steps)[None].expand(B, -1)
+
+    # oracle, fp32
+    h, hk, d = 4, 2, 128
+    x = hidden.reshape(-1, 512)
+    q = (x @ w["q_proj.weight"].T).view(-1, h, d)
+    k = (x @ w["k_proj.weight"].T).view(-1, hk, d)
+    v = (x @ w["v_proj.weight"].T).view(-1, hk, d)
+    cos, sin = orc.rope_cos_sin(pos.reshape(-1), d)
+    q, k = orc.apply_rope(q, cos, sin), orc.apply_rope(k, cos, sin)
+    cu = [0, T + steps, 2 * (T + steps)]
+    o, _ = orc.attention_dense_ref(q, k, v, cu, None, None, torch.ones(q.shape[0], dtype=torch.bool))
+    ref = (o.reshape(-1, 512) @ w["o_proj.weight"].T).view(B, T + steps, 512)
+    tol = 0.08 * ref.std().item()
+
+    hd = hidden.to(cuda_device, torch.bfloat16)
+    with torch.no_grad():
+        full, _, _ = layer(hd, position_ids=pos.to(cuda_device))
+        assert (full.float().cpu() - ref).abs().max().item() <= tol
+        cache = Cache()
+        y, _, past = layer(hd[:, :T], position_ids=pos[:, :T].to(cuda_device), past_key_value=cache, use_cache=True)
+        assert past is cache and (y.float().cpu() - ref[:, :T]).abs().max().item() <= tol
+        for s in range(steps):
+            y, _, _ = layer(hd[:, T + s: T + s + 1], position_ids=pos[:, T + s: T + s + 1].to(cuda_device),
+                            past_key_value=cache, use_cache=True)
+            assert (y.float().cpu() - ref[:, T + s: T + s + 1]).abs().max().item() <= tol
+    assert cache.get_seq_length(0) == T + steps
+
+    # training path: gradients flow to the input and to every projection
+    layer.train()
+    hg = hd[:, :128].clone().requires_grad_(True)
+    out, _, _ = layer(hg, position_ids=pos[:, :128].to(cuda_device))
+    out.float().square().mean().backward()
+    assert hg.grad is not None and torch.isfinite(hg.grad).all()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters())
