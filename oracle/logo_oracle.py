@@ -228,7 +228,7 @@ def logo_layer_ref(
     return_parts: bool = False,
     selection_override: Optional[torch.Tensor] = None,
 ):
-    """logo/layers/logo.py:96-262 with global_qk_param='linear_proj', no cache, no dropout.
+    """logo/layers/logo.py:96-262 (either global_qk_param, chosen by the weight names), no cache, no dropout.
 
     ``weights`` uses the reference's parameter names (q_proj.weight, ..., q_global_proj,
     gate_proj.weight, context_norm_local.weight, context_norm_global.weight, o_proj.weight).
@@ -243,9 +243,14 @@ def logo_layer_ref(
     k = hidden @ weights["k_proj.weight"].T
     v = hidden @ weights["v_proj.weight"].T
     qv, kv, vv = q.view(n, num_heads, d), k.view(n, num_kv_heads, d), v.view(n, num_kv_heads, d)
-    gq = torch.einsum("lhd,hde->lhe", qv, weights["q_global_proj"])   # :86-94
-    gk = torch.einsum("lhd,hde->lhe", kv, weights["k_global_proj"])
-    gv = torch.einsum("lhd,hde->lhe", vv, weights["v_global_proj"])
+    if "q_global_scale" in weights:                                   # global_qk_param='scale_offset', :80-84
+        gq = (q * weights["q_global_scale"] + weights["q_global_offset"]).view(n, num_heads, d)
+        gk = (k * weights["k_global_scale"] + weights["k_global_offset"]).view(n, num_kv_heads, d)
+        gv = (v * weights["v_global_scale"] + weights["v_global_offset"]).view(n, num_kv_heads, d)
+    else:                                                             # 'linear_proj', :86-94
+        gq = torch.einsum("lhd,hde->lhe", qv, weights["q_global_proj"])
+        gk = torch.einsum("lhd,hde->lhe", kv, weights["k_global_proj"])
+        gv = torch.einsum("lhd,hde->lhe", vv, weights["v_global_proj"])
     gate = torch.sigmoid(hidden @ weights["gate_proj.weight"].T)      # :130  [N,1]
     cu_t = torch.as_tensor(cu)
     idx = torch.arange(n)

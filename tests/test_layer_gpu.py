@@ -222,3 +222,48 @@ def test_dense_attention_layer_vs_oracle(cuda_device):
     out.float().square().mean().backward()
     assert hg.grad is not None and torch.isfinite(hg.grad).all()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters())
+
+
+def test_scale_offset_parameterisation_fwd_bwd_vs_oracle(cuda_device):
+    """global_qk_param='scale_offset' (logo/layers/logo.py:44-51,80-84): the layer's output and the
+    gradients of the input and of every parameter against fp32 autograd through the oracle."""
+    from logo_b200 import LoGoAttention
+    from logo_b200.config import LoGoConfig
+
+    cfg = LoGoConfig(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, window_size=128,
+                     global_qk_param="scale_offset", gate_thres_init=0.5, num_hidden_layers=1, rms_norm_eps=1e-5,
+                     max_position_embeddings=4096)
+    torch.manual_seed(21)
+    layer = LoGoAttention(cfg, layer_idx=0)
+    with torch.no_grad():
+        for name, p in layer.named_parameters():
+            if name.endswith("_scale"):
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            elif name.endswith("_offset"):
+                p.copy_(0.1 * torch.randn_like(p))
+            elif "context_norm" in name:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            else:
+                p.normal_(0, 0.05)
+    layer = layer.to(cuda_device, torch.bfloat16).train()
+    lens = [180, 0, 270]
+    n = sum(lens)
+    cu = [0, 180, 180, 450]
+    pos = torch.cat([torch.arange(l) for l in lens])[None]
+    h = torch.randn(1, n, 256).to(torch.bfloat16).to(cuda_device).requires_grad_(True)
+    out, _, _ = layer(h, position_ids=pos.to(cuda_device), cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=cuda_device))
+    d_out = torch.randn(out.shape).to(torch.bfloat16)
+    out.backward(d_out.to(cuda_device))
+
+    gate = torch.sigmoid(layer.gate_proj(h.detach())).float()
+    sel = (gate.reshape(-1) >= 0.5).cpu()
+    assert 0 < int(sel.sum()) < n
+    w = {k: v.detach().float().cpu().requires_grad_(True) for k, v in layer.named_parameters()}
+    hr = h.detach().float().cpu()[0].requires_grad_(True)
+    ref = orc.logo_layer_ref(hr, w, cu, 2, 1, 128, 0.5, 1e-5, selection_override=sel)
+    ref.backward(d_out.float()[0])
+    assert orc.err_ratio(ref.detach(), out[0].float().cpu()) < 2e-2
+    assert orc.err_ratio(hr.grad, h.grad[0].float().cpu()) < 3e-2
+    for name, p in layer.named_parameters():
+        r = orc.err_ratio(w[name].grad, p.grad.float().cpu())
+        assert r < 4e-2, (name, r)
