@@ -3,6 +3,10 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - The device that owns the pointers and the stream must be the calling thread's current
+ *     device (cudaSetDevice) when an entry point is called: launches, the per-device caches
+ *     (SM count, kernel attributes) and the static scratch of logo_select_rows_static all go
+ *     by the current device.
  *   - The caller owns all memory (inputs, outputs, workspaces); the library never
  *     allocates, frees or keeps device memory across calls, and never synchronises
  *     the host with the device. All work is enqueued on `stream`.
@@ -122,6 +126,8 @@ int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int th
  *   - All calls on a device share the one array, and it still holds what the previous call
  *     wrote: the function clears the part it needs on `stream` first. Two calls that can overlap
  *     on the GPU (different streams, or different host threads) race on it -- serialise them.
+ *   - The cached address does not survive cudaDeviceReset: do not call this entry point on a
+ *     device after resetting it.
  * ------------------------------------------------------------------------------------------ */
 #define LOGO_SELECT_STATIC_MAX_TOKENS (1 << 20)
 
@@ -171,9 +177,23 @@ int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* ls
  *   dk, dv [n_tokens, h, 128] bf16: fully written
  *   workspace: logo_attn_bwd_workspace_bytes(n_tokens, hq, gathered) bytes, 256-byte aligned;
  *              gathered = 1 for logo_sq_attn_bwd (packed copies of the selected Q / dO rows,
- *              head-major lse and delta), 0 for logo_swa_bwd (lse and delta only)
+ *              head-major lse and delta, fp32 dQ accumulator), 0 for logo_swa_bwd (lse, delta and
+ *              the accumulator)
+ *
+ * Two implementations exist per branch (0 = global / logo_sq_attn_bwd, 1 = local / logo_swa_bwd),
+ * chosen process-wide with logo_set_backward_mode(branch, mode):
+ *   mode 0  single pass: S and dP are formed once per (query tile, key tile) pair and give dK, dV
+ *           and dQ (five tile products; the reference's two kernels, :141-337, execute seven). dQ is
+ *           summed over key tiles with fp32 reductions in global memory whose order is not fixed,
+ *           so dq may differ between two runs in the last bit of the sum; dk and dv are
+ *           reproducible. Default for branch 0.
+ *   mode 1  two kernels (dK/dV, then dQ), every output accumulated in a fixed order: bit-identical
+ *           results from run to run. Default for branch 1.
  * ------------------------------------------------------------------------------------------ */
 size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered);
+
+int logo_set_backward_mode(int branch, int mode);
+int logo_get_backward_mode(int branch); /* current mode of the branch, -1 for an unknown branch */
 
 int logo_sq_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                      void* dq, void* dk, void* dv, const int64_t* q_idx, const int32_t* pos_ids,
@@ -285,7 +305,8 @@ int logo_decode_attn(const void* q_local, const void* q_global, const void* k_ri
  * stream. logo_profile_read waits for those events, returns per kernel kind the summed device
  * time in ms and the number of launches since the last read, and releases the events.
  *   kind 0 select + finalize, 1 attention forward, 2 backward preprocess,
- *        3 backward dK/dV, 4 backward dQ
+ *        3 backward dK/dV, 4 backward dQ (the two-kernel backward),
+ *        5 single-pass backward, 6 its dQ convert / scatter kernel
  * ------------------------------------------------------------------------------------------ */
 int logo_profile_enable(int on);
 /* Creates the events for `n_launches` timed kernel launches ahead of time (at most 4096), so that a
@@ -300,13 +321,13 @@ int logo_profile_read(double* total_ms, int* launches, int n);
  *   mode 0: C = A * B^T   (A, B both K-major in shared memory)
  *   mode 1: C = A * B     (B row-major [k][n], i.e. MN-major operand)
  *   mode 2: C = A * B     (A staged in tensor memory, B MN-major)
+ *   mode 3: C = A^T * B   (both operands MN-major: rows of a and b are the reduction index)
  *   a, b: bf16 [128][128] row-major; c: fp32 [128][128]
- *   flags bit 0: stage A through thread-written swizzled shared memory instead of TMA.
- *   flags bits 8-23 (timing mode, n > 0): issue the tile product n extra times first and report
- *     in status[1..3] the clocks spent issuing, the clocks until completion and that span in ns;
- *     bit 4: N = 64, bit 3: commit after every product, bit 5: alternate accumulators,
- *     bit 6: first k-step overwrites, bit 7: one elected region per product,
- *     bits 24-31: number of identical CTAs to launch (status / c come from CTA 0).
+ *   flags bit 0 / bit 2: stage A / B through thread-written swizzled shared memory instead of TMA.
+ *   flags bit 3: nothing ever arms the barrier the kernel waits on, so the wait runs out: the kernel
+ *     must return with LOGO_DEV_WAIT_TIMEOUT in `status` and leave c untouched (the test of the
+ *     bounded waits every kernel of this library shares).
+ *   flags bits 8-23: limit of every wait of this launch in microseconds (0: the default, 1 s).
  * ------------------------------------------------------------------------------------------ */
 int logo_umma_selftest(int mode, int flags, const void* a, const void* b, float* c, uint32_t lbo_bytes,
                        uint32_t sbo_bytes, uint32_t kstep_bytes, int32_t* status, logo_stream_t stream);

@@ -13,9 +13,11 @@ no Triton, flash-attn or CPU path.
 """
 from . import ops
 from .cache import Cache
-from .layers import Attention, LoGoAttention
+from .layers import Attention, LoGoAttention, check_status
 from .ops import SelInfo, build_selection, sq_full_attn
+from .ops_bwd import get_backward_mode, set_backward_mode
 from .update import update_gate_thres
 
-__all__ = ["ops", "Attention", "Cache", "LoGoAttention", "SelInfo", "build_selection", "sq_full_attn", "update_gate_thres"]
+__all__ = ["ops", "Attention", "Cache", "LoGoAttention", "SelInfo", "build_selection", "check_status",
+           "get_backward_mode", "set_backward_mode", "sq_full_attn", "update_gate_thres"]
 __version__ = "0.1.0"

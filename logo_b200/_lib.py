@@ -37,6 +37,8 @@ _SIGNATURES = {
                                                    c_void_p]),
     "logo_swa_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     "logo_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "logo_set_backward_mode": (c_int, [c_int, c_int]),
+    "logo_get_backward_mode": (c_int, [c_int]),
     "logo_sq_attn_bwd": (c_int, [c_void_p] * 16 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                                    c_void_p]),
     "logo_swa_bwd": (c_int, [c_void_p] * 13 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
@@ -117,6 +119,17 @@ def torch_dtype_code(dtype) -> int:
     if dtype not in table:
         raise TypeError(f"unsupported dtype {dtype}")
     return table[dtype]
+
+
+def on_device(t):
+    """Context manager that makes the device of tensor ``t`` current for the enclosed C-ABI calls.
+
+    The library launches on, and keys its per-device caches by, the calling thread's current
+    device; a tensor on ``cuda:1`` while ``cuda:0`` is current would otherwise hand the library a
+    stream of another device."""
+    import torch
+
+    return torch.cuda.device(t.device)
 
 
 def current_stream_ptr(device) -> int:

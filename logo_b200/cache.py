@@ -111,17 +111,46 @@ class Cache:
             b, h, t_new, d = k_global.shape
         cur = self.layers[layer_idx].length if layer_idx < len(self.layers) else 0
         st = self._ensure(layer_idx, b, h, d, window if k_local is not None else None, cur + t_new, k_global.device)
-        rc = lib.logo_cache_append(_lib.ptr(k_local), _lib.ptr(v_local), k_global.data_ptr(), v_global.data_ptr(),
-                                   ref_strides[0], ref_strides[1], ref_strides[2],
-                                   _lib.ptr(st.k_ring) if k_local is not None else None,
-                                   _lib.ptr(st.v_ring) if k_local is not None else None, st.ring,
-                                   st.k_full.data_ptr(), st.v_full.data_ptr(), st.t_max, None, st.length, b, t_new, h,
-                                   d, st.status.data_ptr(), _lib.current_stream_ptr(k_global.device))
+        if k_local is not None and st.k_ring is not None and st.ring != window + 1:
+            self._resize_ring(st, window)
+        with _lib.on_device(k_global):
+            rc = self._append_call(lib, st, k_local, v_local, k_global, v_global, ref_strides, b, t_new, h, d)
         _lib.check(rc, "logo_cache_append")
         st.length += t_new
         if layer_idx == 0:
             self._seen_tokens += t_new
         return st
+
+    @staticmethod
+    def _append_call(lib, st, k_local, v_local, k_global, v_global, ref_strides, b, t_new, h, d) -> int:
+        return lib.logo_cache_append(_lib.ptr(k_local), _lib.ptr(v_local), k_global.data_ptr(), v_global.data_ptr(),
+                                   ref_strides[0], ref_strides[1], ref_strides[2],
+                                   _lib.ptr(st.k_ring) if k_local is not None else None,
+                                   _lib.ptr(st.v_ring) if k_local is not None else None, st.ring,
+                                   st.k_full.data_ptr(), st.v_full.data_ptr(), st.t_max, None, st.length, b, t_new, h,
+                                   d, st.status.data_ptr(), _lib.current_stream_ptr(k_global.device))
+
+    @staticmethod
+    def _resize_ring(st: _LayerState, window: int) -> None:
+        """Re-lays the local ring for another window size (a cache built from a legacy tuple does not
+        know the layer's window until the first append). The ring holds local-branch states, which
+        cannot be recomputed from the global state: tokens the old ring no longer holds are lost, so a
+        ring that is too small for the new window is an error, not a silent truncation."""
+        have = min(st.length, st.ring)                 # last tokens present in the old ring
+        need = min(st.length, window)                  # tokens a step with this window attends over
+        if have < need:
+            raise ValueError(f"the cached local state holds {have} tokens but window_size {window} needs {need}; "
+                             "rebuild the cache with the layer's window_size")
+        keep = min(have, window + 1)
+        pos = torch.arange(st.length - keep, st.length, device=st.k_ring.device)
+        new_ring = window + 1
+        for name in ("k_ring", "v_ring"):
+            old = getattr(st, name)
+            new = torch.zeros(old.shape[0], old.shape[1], new_ring, old.shape[3], dtype=old.dtype, device=old.device)
+            if keep:
+                new.index_copy_(2, pos % new_ring, old.index_select(2, pos % st.ring))
+            setattr(st, name, new)
+        st.ring = new_ring
 
     def layer_buffers(self, layer_idx: int) -> _LayerState:
         return self.layers[layer_idx]
@@ -202,8 +231,11 @@ class Cache:
                     raise NotImplementedError("legacy states must hold both attn_state and attn_state_full")
                 t = full[0].shape[-2]
                 w = local[0].shape[-2]
-                # the legacy local state holds the last `w` tokens; rebuild the ring from it
-                window = window_size or max(w, 128)
+                # The legacy local state holds the last `w` = min(t, window) tokens. Without an explicit
+                # window_size the ring is sized for exactly those; the first append() passes the layer's
+                # real window and re-lays the ring if it differs (nothing is lost: when t > w, w IS the
+                # window; when t == w every cached token is in the state).
+                window = window_size or max(w, 1)
                 st = cache._ensure(layer_idx, full[0].shape[0], full[0].shape[1], full[0].shape[-1], window, t,
                                    full[0].device)
                 st.k_full[:, :, :t].copy_(full[0])

@@ -20,134 +20,11 @@
 //
 // Algorithmic work: 2.5x the forward FLOPs (5 products against 2); S is recomputed in both
 // GEMM kernels, so 7 products execute.
-#include "attn_common.cuh"
-#include "host_common.cuh"
+#include "attn_bwd_common.cuh"
+
+#include <atomic>
 
 namespace logo {
-
-struct BwdArgs {
-  const int64_t* q_idx;       // null: identity (local branch)
-  const int32_t* pos_ids;
-  const int32_t* cu_q;
-  const int32_t* cu_k;
-  const int32_t* tile_off_q;  // [n_seq+1] prefix of 128-row query tiles
-  const int32_t* n_qtiles;
-  const int32_t* tile_off_k;  // [n_seq+1] prefix of 128-key tiles
-  const int32_t* n_ktiles;
-  int* counter_dq;            // [1] zeroed before the launch: next unclaimed item of the dQ kernel
-  int* counter_dkv;           // [1] same for the dK/dV kernel
-  const float* lse_sel;       // [hq][cap] head-major, compact rows
-  const float* delta_sel;     // [hq][cap]
-  int cap;
-  __nv_bfloat16* dq;          // [n_tokens, hq, 128]
-  __nv_bfloat16* dk;          // [n_tokens, h, 128]
-  __nv_bfloat16* dv;
-  int n_seq, n_tokens, hq, h, window;
-  float scale, scale_log2;
-  int* status;
-};
-
-constexpr int BWD_THREADS = 320;      // dK/dV kernel: 8 element-wise warps + producer + MMA
-constexpr int DQ_EW_WARPS = 16;        // dQ kernel: 16 element-wise warps (four per scheduler), 32 columns each
-constexpr int DQ_THREADS = (DQ_EW_WARPS + 2) * 32;
-constexpr int BWD_SMEM_BYTES = 6 * TILE_BYTES + 1024;
-
-__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-__device__ __forceinline__ int bwd_row_position(const BwdArgs& a, int bos_q, int r) {
-  return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;
-}
-
-
-// r[i] <- bits of p = 2^(s*c - lse) for 32 scores of one row; keys outside [key_lo, key_hi] give 0.
-// MASK is a template parameter so that the unmasked (by far most frequent) instance is branch-free:
-// 0 no mask, 1 causal only (one comparison per element), 2 causal + window.
-template <int MASK>
-__device__ __forceinline__ void prob_chunk_row_t(uint32_t (&r)[32], float c, float lse, int k0, int key_hi, int key_lo) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float pv = fast_exp2(fmaf(__uint_as_float(r[i]), c, -lse));
-    if (MASK == 1) pv = (k0 + i <= key_hi) ? pv : 0.f;
-    if (MASK == 2) pv = (k0 + i <= key_hi && k0 + i >= key_lo) ? pv : 0.f;
-    r[i] = __float_as_uint(pv);
-  }
-}
-
-__device__ __forceinline__ void prob_chunk_row(uint32_t (&r)[32], float c, float lse, bool masked, int k0, int key_hi,
-                                               int key_lo) {
-  if (!masked) prob_chunk_row_t<0>(r, c, lse, k0, key_hi, key_lo);
-  else if (key_lo == INT32_MIN) prob_chunk_row_t<1>(r, c, lse, k0, key_hi, key_lo);
-  else prob_chunk_row_t<2>(r, c, lse, k0, key_hi, key_lo);
-}
-
-// pk[i] <- bf16x2 of p * (dp - delta) for 32 elements of one row
-__device__ __forceinline__ void ds_pack_chunk_row(const uint32_t (&p)[32], const uint32_t (&dp)[32], float delta,
-                                                  uint32_t* pk) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float d0 = __uint_as_float(p[2 * i]) * (__uint_as_float(dp[2 * i]) - delta);
-    const float d1 = __uint_as_float(p[2 * i + 1]) * (__uint_as_float(dp[2 * i + 1]) - delta);
-    pk[i] = pack_bf16x2(d0, d1);
-  }
-}
-
-// Column-wise variants for the transposed tiles of the dK/dV kernel: lse / delta / position differ per
-// column and come from shared memory (16-byte broadcast loads). MASK as above; an invalid key row
-// (past the end of the sequence) is passed as key_pos = INT32_MAX, which no query position reaches.
-template <int MASK>
-__device__ __forceinline__ void prob_chunk_col_t(uint32_t (&r)[32], float c, const float* __restrict__ lse_s,
-                                                 const int* __restrict__ pos_s, int key_pos, int window) {
-#pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 4 * g);
-    const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-    int pv4[4] = {0, 0, 0, 0};
-    if (MASK != 0) {
-      const int4 q4 = *reinterpret_cast<const int4*>(pos_s + 4 * g);
-      pv4[0] = q4.x;
-      pv4[1] = q4.y;
-      pv4[2] = q4.z;
-      pv4[3] = q4.w;
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float pv = fast_exp2(fmaf(__uint_as_float(r[4 * g + e]), c, -lv[e]));
-      if (MASK == 1) pv = (key_pos <= pv4[e]) ? pv : 0.f;
-      if (MASK == 2) pv = (key_pos <= pv4[e] && key_pos >= pv4[e] - window) ? pv : 0.f;
-      r[4 * g + e] = __float_as_uint(pv);
-    }
-  }
-}
-
-__device__ __forceinline__ void prob_chunk_col(uint32_t (&r)[32], float c, const float* __restrict__ lse_s,
-                                               const int* __restrict__ pos_s, bool masked, bool key_valid,
-                                               int key_pos, int window) {
-  const int kp = key_valid ? key_pos : INT32_MAX;
-  if (!masked) prob_chunk_col_t<0>(r, c, lse_s, pos_s, kp, window);
-  else if (window == 0) prob_chunk_col_t<1>(r, c, lse_s, pos_s, kp, window);
-  else prob_chunk_col_t<2>(r, c, lse_s, pos_s, kp, window);
-}
-
-__device__ __forceinline__ void ds_pack_chunk_col(const uint32_t (&p)[32], const uint32_t (&dp)[32],
-                                                  const float* __restrict__ delta_s, uint32_t* pk) {
-#pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    const float4 d4 = *reinterpret_cast<const float4*>(delta_s + 4 * g);
-    const float d0 = __uint_as_float(p[4 * g]) * (__uint_as_float(dp[4 * g]) - d4.x);
-    const float d1 = __uint_as_float(p[4 * g + 1]) * (__uint_as_float(dp[4 * g + 1]) - d4.y);
-    const float d2 = __uint_as_float(p[4 * g + 2]) * (__uint_as_float(dp[4 * g + 2]) - d4.z);
-    const float d3 = __uint_as_float(p[4 * g + 3]) * (__uint_as_float(dp[4 * g + 3]) - d4.w);
-    pk[2 * g] = pack_bf16x2(d0, d1);
-    pk[2 * g + 1] = pack_bf16x2(d2, d3);
-  }
-}
-
-__device__ __forceinline__ void pack_chunk(const uint32_t (&p)[32], uint32_t* pk) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(p[2 * i]), __uint_as_float(p[2 * i + 1]));
-}
 
 // ---------------------------------------------------------------------------------------
 // 1. preprocess
@@ -157,8 +34,8 @@ __global__ void __launch_bounds__(256)
                           const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
                           const int64_t* __restrict__ q_idx, const int32_t* __restrict__ sq_ptr,
                           __nv_bfloat16* __restrict__ q_sel, __nv_bfloat16* __restrict__ do_sel,
-                          float* __restrict__ lse_sel, float* __restrict__ delta_sel, int cap, int n_tokens, int hq,
-                          int* status) {
+                          float* __restrict__ lse_sel, float* __restrict__ delta_sel, float* __restrict__ dq_acc,
+                          int cap, int n_tokens, int hq, int* status) {
   const bool gathered = (q_idx != nullptr);
   const int sq = gathered ? min(max(__ldg(sq_ptr), 0), n_tokens) : n_tokens;
   const int rows_total = gathered ? min(sq + TILE, cap) : sq;
@@ -212,6 +89,11 @@ __global__ void __launch_bounds__(256)
               const size_t dst = ((size_t)r * hq + hh[u]) * HEAD_DIM + col;
               *reinterpret_cast<uint4*>(q_sel + dst) = qv[u];
               *reinterpret_cast<uint4*>(do_sel + dst) = dv[u];
+            }
+            if (dq_acc) {   // the single-pass backward adds into this row: it must start at zero
+              float4* z = reinterpret_cast<float4*>(dq_acc + ((size_t)r * hq + hh[u]) * HEAD_DIM + col);
+              z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+              z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
           }
         }
@@ -548,44 +430,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
 // ---------------------------------------------------------------------------------------
 // 3. dK / dV
 // ---------------------------------------------------------------------------------------
-struct DkvItem {
-  int kvh, bos_q, bos_k, nsel, len_k, kv_start, i0, i_end;
-};
-
-// first index in [0, n) with pos[idx] >= x (pos ascending)
-__device__ __forceinline__ int lower_bound_pos(const int32_t* __restrict__ pos, int n, int x) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (__ldg(pos + mid) < x) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
-
-__device__ __forceinline__ void dkv_decode_item(const BwdArgs& a, int w, DkvItem& it) {
-  const int tile_g = w / a.h;
-  it.kvh = w % a.h;
-  const int seq = find_sequence(a.tile_off_k, a.n_seq, tile_g);
-  const int tile_l = tile_g - __ldg(a.tile_off_k + seq);
-  it.bos_q = __ldg(a.cu_q + seq);
-  it.nsel = max(__ldg(a.cu_q + seq + 1) - it.bos_q, 0);
-  it.bos_k = __ldg(a.cu_k + seq);
-  it.len_k = __ldg(a.cu_k + seq + 1) - it.bos_k;
-  it.kv_start = tile_l * TILE;
-  int first, last;  // compacted rows [first, last) can see some key of this tile
-  if (a.q_idx) {
-    const int32_t* pos = a.pos_ids + it.bos_q;
-    first = lower_bound_pos(pos, it.nsel, it.kv_start);
-    last = a.window > 0 ? lower_bound_pos(pos, it.nsel, it.kv_start + TILE + a.window) : it.nsel;
-  } else {
-    first = min(it.kv_start, it.nsel);
-    last = a.window > 0 ? min(it.nsel, it.kv_start + TILE + a.window) : it.nsel;
-  }
-  it.i0 = first / TILE;
-  it.i_end = (last + TILE - 1) / TILE;
-  if (last <= first) it.i_end = it.i0;
-}
-
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -967,6 +811,7 @@ struct BwdWorkspace {
   __nv_bfloat16* do_sel;
   float* lse_sel;
   float* delta_sel;
+  float* dq_acc;      // [cap][hq][128] fp32 accumulator of the single-pass backward
   int cap;
   size_t bytes;
 };
@@ -988,9 +833,15 @@ static BwdWorkspace bwd_workspace_layout(void* base, int n_tokens, int hq, bool 
   }
   w.lse_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
   w.delta_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
+  w.dq_acc = reinterpret_cast<float*>(take((size_t)w.cap * hq * HEAD_DIM * 4));
   w.bytes = off;
   return w;
 }
+
+// Which backward runs, per branch (0 = global / query-sparse, 1 = local / window):
+// 0 single pass (five tile products, dQ by fp32 reductions), 1 two kernels (seven products, every
+// output accumulated in a fixed order).
+static std::atomic<int> g_bwd_mode[2] = {{0}, {1}};
 
 static int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                            const void* d_o, void* dq, void* dk, void* dv, const int64_t* q_idx,
@@ -1010,12 +861,13 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
                                                 (size_t)hq * HEAD_DIM * sizeof(__nv_bfloat16), stream);
     if (rc0) return rc0;
   }
+  const bool fused = g_bwd_mode[gathered ? 0 : 1].load(std::memory_order_relaxed) == 0;
 
   const int sms = sm_count();
   prof_begin(PROF_BWD_PRE, stream);
   bwd_preprocess_kernel<<<sms * 4, 256, 0, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, q_idx, sq_ptr, ws.q_sel,
-      ws.do_sel, ws.lse_sel, ws.delta_sel, ws.cap, n_tokens, hq, status);
+      ws.do_sel, ws.lse_sel, ws.delta_sel, fused ? ws.dq_acc : nullptr, ws.cap, n_tokens, hq, status);
   prof_end(PROF_BWD_PRE, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
 
@@ -1029,17 +881,6 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   if ((rc = make_tmap_2d_bf16(&tm_do, do_src, (uint64_t)hq * HEAD_DIM, q_rows, q_row_bytes, 64, TILE))) return rc;
   if ((rc = make_tmap_2d_bf16(&tm_k, k, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
   if ((rc = make_tmap_2d_bf16(&tm_v, v, (uint64_t)h * HEAD_DIM, (uint64_t)n_tokens, kv_row_bytes, 64, TILE))) return rc;
-
-  static thread_local int attr_set_dev = -1;
-  int dev = 0;
-  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
-  if (attr_set_dev != dev) {
-    LOGO_CHECK_CUDA(
-        cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
-    LOGO_CHECK_CUDA(
-        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
-    attr_set_dev = dev;
-  }
 
   BwdArgs a{};
   a.q_idx = q_idx;
@@ -1067,6 +908,18 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
 
+  if (fused) return launch_attn_bwd_fused(tm_q, tm_do, tm_k, tm_v, a, ws.dq_acc, sq_ptr, stream);
+
+  static thread_local int attr_set_dev = -1;
+  int dev = 0;
+  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (attr_set_dev != dev) {
+    LOGO_CHECK_CUDA(
+        cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+    LOGO_CHECK_CUDA(
+        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+    attr_set_dev = dev;
+  }
   LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dq, 0, sizeof(int), stream));
   LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dkv, 0, sizeof(int), stream));
   prof_begin(PROF_BWD_DKV, stream);
@@ -1081,6 +934,18 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
 }
 
 }  // namespace logo
+
+extern "C" int logo_set_backward_mode(int branch, int mode) {
+  using namespace logo;
+  LOGO_REQUIRE(branch == 0 || branch == 1, LOGO_ERR_INVALID, "branch must be 0 (global) or 1 (local), got %d", branch);
+  LOGO_REQUIRE(mode == 0 || mode == 1, LOGO_ERR_INVALID, "mode must be 0 (single pass) or 1 (two kernels), got %d", mode);
+  g_bwd_mode[branch].store(mode, std::memory_order_relaxed);
+  return LOGO_OK;
+}
+
+extern "C" int logo_get_backward_mode(int branch) {
+  return (branch == 0 || branch == 1) ? logo::g_bwd_mode[branch].load(std::memory_order_relaxed) : -1;
+}
 
 extern "C" size_t logo_attn_bwd_workspace_bytes(int n_tokens, int hq, int gathered) {
   if (n_tokens < 0 || hq <= 0) return 0;

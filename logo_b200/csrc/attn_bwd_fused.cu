@@ -1,0 +1,528 @@
+// Single-pass backward attention: dK, dV and dQ from ONE evaluation of S and dP per
+// (query tile, key tile) pair, five tile products instead of the seven of the two-kernel path.
+//
+// Work item = (128-key tile, kv head); the CTA keeps the K / V tile in shared memory and the
+// dK / dV accumulators in tensor memory and streams the Q / dO tiles of every query head of
+// the group that can see the key tile. Per step (one query tile):
+//     S^T  = K Q^T            -> TMEM X           (both operands K-major in shared memory)
+//     dP^T = V dO^T           -> TMEM Y
+//     P^T  = exp2(S^T c - lse) masked, bf16       -> written into X (the A operand of dV)
+//     dV  += P^T dO                               (A from TMEM, B = dO tile read MN-major)
+//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory as a [key][query]
+//                                                    tile, into the dO stage dV has finished with
+//     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
+//     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
+// dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
+// dedicated warps and added to an fp32 accumulator in global memory with red.global.add
+// (32 lanes = 32 consecutive floats of one query row: one 128-byte reduction per instruction);
+// bwd_dq_finish_kernel scales, converts and scatters it to the token rows afterwards.
+// Tensor memory is full (X, Y, dK, dV = 512 columns): dQ^T shares Y with dP^T, so the next
+// dP^T waits until the read-out warps hold the previous dQ^T in registers.
+//
+// Warp roles (448 threads): 0-7 element-wise (lane quarter w % 4, 64 query columns each),
+// 8-11 dQ read-out (one per lane quarter), 12 TMA producer + work claiming, 13 MMA issue.
+//
+// The order in which key tiles reach a dQ row is not fixed, so dQ can differ between runs in
+// the last bit of its fp32 sum (dK and dV are accumulated in a fixed order and are reproducible).
+#include "attn_bwd_common.cuh"
+
+namespace logo {
+
+constexpr int FUSED_EW_WARPS = 8;
+constexpr int FUSED_DQ_WARPS = 4;
+constexpr int FUSED_THREADS = (FUSED_EW_WARPS + FUSED_DQ_WARPS + 2) * 32;
+
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+  asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+// 448 threads x 144 registers = 63 K of the 64 K register file (a launch bound of 448 threads alone
+// makes the compiler budget for 512 and stop at 128 registers, which spills)
+__global__ void __maxnreg__(144)
+    attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                          const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                          const BwdArgs a, float* __restrict__ dq_acc) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;    // 2 stages
+  uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages; stage s & 1 holds dS^T of step s once dV(s) is done
+
+  __shared__ uint64_t kv_full, kv_free, q_full[2], do_full[2], qdo_empty[2];
+  __shared__ uint64_t st_full, dpt_full, p_ready, dv_done, ds_ready, dq_full, dq_read, acc_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) float s_lse[2][TILE];
+  __shared__ __align__(16) float s_delta[2][TILE];
+  __shared__ __align__(16) int s_pos[2][TILE];
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
+
+  const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
+  AbortState ab{&abort_flag, a.status};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&kv_full, 1);
+    mbar_init(&kv_free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(&st_full, 1);
+    mbar_init(&dpt_full, 1);
+    mbar_init(&p_ready, FUSED_EW_WARPS);    // one arrival per warp
+    mbar_init(&dv_done, 1);
+    mbar_init(&ds_ready, FUSED_EW_WARPS);
+    mbar_init(&dq_full, 1);
+    mbar_init(&dq_read, FUSED_DQ_WARPS);
+    mbar_init(&acc_done, 1);
+    ring_init(ring, FUSED_EW_WARPS + FUSED_DQ_WARPS + 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t TM_X = tmem, TM_Y = tmem + 128u, TM_DK = tmem + 256u, TM_DV = tmem + 384u;
+
+  const int total_tiles = __ldg(a.n_ktiles);
+  const long long total_items = (long long)total_tiles * a.h;
+  const int G = a.hq / a.h;
+
+  if (warp < FUSED_EW_WARPS) {
+    // ================= element-wise warps =================
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;   // key inside the tile
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int col0 = half * 64;
+    const float c = a.scale_log2;
+    uint32_t idx = 0, n_items = 0;
+
+    // lse / delta / pos of query tile `i` of head `hq`, loaded unconditionally from a clamped row
+    const int vrow = tid & (TILE - 1);
+    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) -> bool {
+      const int r = i * TILE + vrow;
+      const int rc = min(r, it.nsel - 1);
+      const size_t sidx = (size_t)hq * a.cap + it.bos_q + rc;
+      l = __ldg(a.lse_sel + sidx);
+      d = __ldg(a.delta_sel + sidx);
+      p = bwd_row_position(a, it.bos_q, rc);
+      return r < it.nsel;
+    };
+
+    uint32_t n_ring = 0;
+    DkvItem it;
+    long long w = ring_pop(ring, n_ring, it, ab);
+    bool vec_ready = false;   // the first-step vectors of `it` are already in s_*[idx & 1]
+    while (w >= 0) {
+      DkvItem it_next;
+      long long w_next = -1;
+      bool vec_next = false;
+      const int nq = it.i_end - it.i0;
+      const int key_pos = it.kv_start + row;
+      const bool key_valid = key_pos < it.len_k;
+      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      if (nq <= 0) {
+        // no query can see this key tile: the gradients are zero
+        if (key_valid) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            reinterpret_cast<uint4*>(dk_row)[g] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(dv_row)[g] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        w_next = ring_pop(ring, n_ring + 1, it_next, ab);
+        ring_release(ring, n_ring);
+        it = it_next;
+        w = w_next;
+        vec_ready = false;
+        ++n_ring;
+        continue;
+      }
+      const int n_steps = nq * G;
+      const bool partial_keys = it.kv_start + TILE > it.len_k;
+
+      if (!vec_ready) {
+        float l, d;
+        int p;
+        const bool ok = fetch_vec(it, it.kvh * G, it.i0, l, d, p);
+        if (tid < TILE) {
+          s_lse[idx & 1u][tid] = ok ? l : 0.f;
+          s_delta[idx & 1u][tid] = ok ? d : 0.f;
+          s_pos[idx & 1u][tid] = ok ? p : -1;
+        }
+        named_barrier_sync(3, 256);
+      }
+
+      int g_nx = 0, i_nx = 0;   // (head of the group, query tile) of step s + 1
+      for (int s = 0; s < n_steps; ++s, ++idx) {
+        if (++i_nx == nq) {
+          i_nx = 0;
+          ++g_nx;
+        }
+        const uint32_t vb = idx & 1u;
+        // the vectors of the next step travel global -> shared asynchronously (the buffer they land
+        // in was last read before the named barrier of the previous step)
+        const bool has_next = (s + 1 < n_steps);
+        bool next_ok = true;
+        if (!has_next) {
+          w_next = ring_pop(ring, n_ring + 1, it_next, ab);
+          vec_next = (w_next >= 0) && (it_next.i_end > it_next.i0);
+        }
+        if ((has_next || vec_next) && tid < TILE) {
+          const DkvItem& src = has_next ? it : it_next;
+          const int hq_nx = src.kvh * G + (has_next ? g_nx : 0);
+          const int r = (src.i0 + (has_next ? i_nx : 0)) * TILE + tid;
+          const int rc = min(r, src.nsel - 1);
+          next_ok = r < src.nsel;
+          const size_t sidx = (size_t)hq_nx * a.cap + src.bos_q + rc;
+          cp_async_4(&s_lse[vb ^ 1u][tid], a.lse_sel + sidx);
+          cp_async_4(&s_delta[vb ^ 1u][tid], a.delta_sel + sidx);
+          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + src.bos_q + rc);
+          else s_pos[vb ^ 1u][tid] = next_ok ? r : -1;
+        }
+
+        const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
+        const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
+                            (a.window > 0 && pos_last > it.kv_start + a.window);
+        uint32_t p0[32], p1[32];
+        mbar_wait(&st_full, idx & 1u, ab);
+        tc_fence_after();
+        tmem_ld32(TM_X + lane_off + (uint32_t)col0, p0);
+        tmem_ld32(TM_X + lane_off + (uint32_t)col0 + 32, p1);
+        tmem_ld_wait();
+        prob_chunk_col(p0, c, &s_lse[vb][col0], &s_pos[vb][col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p1, c, &s_lse[vb][col0 + 32], &s_pos[vb][col0 + 32], masked, key_valid, key_pos, a.window);
+        {
+          uint32_t pk[32];
+          pack_chunk(p0, pk);
+          pack_chunk(p1, pk + 16);
+          // P^T (bf16) overwrites the first 32 of the 64 S^T columns this warp has just read
+          tmem_st32(TM_X + lane_off + (uint32_t)col0, pk);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive_warp(&p_ready);
+        }
+        mbar_wait(&dpt_full, idx & 1u, ab);
+        tc_fence_after();
+        uint32_t ds[32];   // dS^T of this thread's key row, 64 query columns, packed bf16
+        {
+          uint32_t d0[32];
+          tmem_ld32(TM_Y + lane_off + (uint32_t)col0, d0);
+          tmem_ld_wait();
+          ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], ds);
+        }
+        {
+          uint32_t d1[32];
+          tmem_ld32(TM_Y + lane_off + (uint32_t)col0 + 32, d1);
+          tmem_ld_wait();
+          ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], ds + 16);
+        }
+        tc_fence_before();   // Y has been read: after ds_ready the MMA warp may overwrite it with dQ^T
+        if ((has_next || vec_next) && tid < TILE) {
+          cp_async_wait_all();
+          if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
+        }
+        named_barrier_sync(2, 256);   // vector buffers: this step's reads done, next step's values visible
+        // dS^T goes into the dO stage of this step as a [key][query] tile (two [128][64] blocks,
+        // 128-byte swizzled): dV(s) was the last reader of the dO tile
+        mbar_wait(&dv_done, idx & 1u, ab);
+        {
+          uint8_t* dst = sDO + (idx & 1u) * TILE_BYTES + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(dst + (((uint32_t)ch ^ ((uint32_t)row & 7u)) << 4)) =
+                make_uint4(ds[4 * ch], ds[4 * ch + 1], ds[4 * ch + 2], ds[4 * ch + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&ds_ready);
+      }
+
+      // ---- epilogue: dK * scale, dV -> bf16 rows ----
+      mbar_wait(&acc_done, n_items & 1u, ab);
+      tc_fence_after();
+      ++n_items;
+      {
+        const long long row_off =
+            key_valid ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0) : -1;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
+          const float mul = (which == 0) ? a.scale : 1.f;
+#pragma unroll
+          for (int chk = 0; chk < 2; ++chk) {
+            uint32_t r[32], pk[16];
+            tmem_ld32(base + chk * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
+            store_patch_32x32(s_stage[warp], pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+          }
+        }
+      }
+      tc_fence_before();
+      ring_release(ring, n_ring);
+      it = it_next;
+      w = w_next;
+      vec_ready = vec_next;
+      ++n_ring;
+    }
+  } else if (warp < FUSED_EW_WARPS + FUSED_DQ_WARPS) {
+    // ================= dQ read-out warps =================
+    // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
+    // and the 128 query rows of the step as columns.
+    const int quad = warp & 3;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const size_t row_stride = (size_t)a.hq * HEAD_DIM;   // floats between consecutive query rows of dq_acc
+    uint32_t idx = 0;
+    for (uint32_t n_ring = 0;; ++n_ring) {
+      DkvItem it;
+      const long long w = ring_pop(ring, n_ring, it, ab);
+      if (w < 0) break;
+      const int nq = it.i_end - it.i0;
+      if (nq <= 0) {
+        ring_release(ring, n_ring);
+        continue;
+      }
+      for (int g = 0; g < G; ++g) {
+        for (int i = it.i0; i < it.i_end; ++i, ++idx) {
+          const int hq = it.kvh * G + g;
+          const int nvalid = min(it.nsel - i * TILE, TILE);
+          float* base = dq_acc + ((size_t)(it.bos_q + i * TILE) * a.hq + hq) * HEAD_DIM + quad * 32 + lane;
+          const bool ok = mbar_wait(&dq_full, idx & 1u, ab);
+          tc_fence_after();
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tmem_ld32(TM_Y + lane_off, r0);
+          tmem_ld32(TM_Y + lane_off + 32u, r1);
+          tmem_ld32(TM_Y + lane_off + 64u, r2);
+          tmem_ld32(TM_Y + lane_off + 96u, r3);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
+          if (ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) red_add_f32(base + (size_t)j * row_stride, __uint_as_float(r0[j]));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (32 + j < nvalid) red_add_f32(base + (size_t)(32 + j) * row_stride, __uint_as_float(r1[j]));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (64 + j < nvalid) red_add_f32(base + (size_t)(64 + j) * row_stride, __uint_as_float(r2[j]));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (96 + j < nvalid) red_add_f32(base + (size_t)(96 + j) * row_stride, __uint_as_float(r3[j]));
+          }
+        }
+      }
+      ring_release(ring, n_ring);
+    }
+  } else if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS) {
+    // ================= producer: claims and decodes items, issues the TMA loads =================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      uint32_t q_iter = 0, n_items = 0, n_pub = 0;
+      DkvItem it, it_ahead;
+      long long w_last = -1;
+      auto next_item = [&](DkvItem& dst) -> bool {
+        const long long w = ring_claim(a.counter_dkv, total_items, ab);
+        if (w >= 0) dkv_decode_item(a, (int)w, dst);
+        ring_publish(ring, n_pub++, w, dst, ab);
+        w_last = w;
+        return w >= 0;
+      };
+      bool have = next_item(it);
+      while (have) {
+        const int nq = max(it.i_end - it.i0, 0);
+        if (nq > 0) {
+          const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
+          mbar_wait(&kv_free, (n_items & 1u) ^ 1u, ab);
+          mbar_arrive_expect_tx(&kv_full, 2 * TILE_BYTES);
+          tma_load_2d(sK, &tm_k, &kv_full, xk, yk);
+          tma_load_2d(sK + BLK_BYTES, &tm_k, &kv_full, xk + 64, yk);
+          tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
+          tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
+          ++n_items;
+        }
+        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
+        bool have_ahead = ahead ? next_item(it_ahead) : false;
+        int g = 0, i = it.i0;   // query head of the group, query tile
+        for (int s = 0; s < nq * G; ++s, ++q_iter, ++i) {
+          if (i == it.i_end) {
+            i = it.i0;
+            ++g;
+          }
+          const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+          const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
+          // the stage is free once dK and dQ^T of the step that used it (they read Q and dS^T) are done
+          mbar_wait(&qdo_empty[st], ph ^ 1u, ab);
+          mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
+          tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
+          tma_load_2d(sQ + st * TILE_BYTES + BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
+          mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
+          tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
+          tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
+        }
+        if (!ahead) have_ahead = next_item(it_ahead);
+        it = it_ahead;
+        have = have_ahead;
+      }
+      if (abort_flag) {   // let copies in flight land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    // ================= MMA issuer: the whole warp walks this code, an elected lane issues =================
+    const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // S^T, dP^T: both operands K-major
+    const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // dV, dK: B operand MN-major
+    const uint32_t idesc_mm = umma_idesc_bf16(HEAD_DIM, TILE, 1, 1);   // dQ^T: both operands MN-major
+    const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+    uint32_t q_iter = 0, n_items = 0;
+
+    auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
+      umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
+                                   idesc_kk, 0u);
+    };
+    auto issue_dv = [&](uint32_t a_tmem, uint32_t b_base, bool acc) {
+      umma_tile_k128<true, true, 2>(TM_DV, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
+    };
+    auto issue_dk = [&](uint32_t ds_base, uint32_t b_base, bool acc) {
+      umma_tile_k128<false, true>(TM_DK, umma_desc_sw128(ds_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
+                                  idesc_mn, acc ? 1u : 0u);
+    };
+    auto issue_dq = [&](uint32_t ds_base) {
+      umma_tile_k128<false, true, 0, 0, 8, true>(TM_Y, umma_desc_sw128(k_base, BLK_BYTES, 1024),
+                                                 umma_desc_sw128(ds_base, BLK_BYTES, 1024), idesc_mm, 0u);
+    };
+
+    for (uint32_t n_ring = 0;; ++n_ring) {
+      DkvItem it;
+      const long long w = ring_pop(ring, n_ring, it, ab);
+      if (w < 0) break;
+      const int nq = it.i_end - it.i0;
+      if (nq <= 0) {
+        ring_release(ring, n_ring);
+        continue;
+      }
+      const int n_steps = nq * G;
+      mbar_wait(&kv_full, n_items & 1u, ab);
+      ++n_items;
+      tc_fence_after();
+      {
+        const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+        mbar_wait(&q_full[st], ph, ab);
+        tc_fence_after();
+        issue_kk(TM_X, k_base, q_base + st * TILE_BYTES);
+        umma_commit(&st_full);
+        mbar_wait(&do_full[st], ph, ab);
+        // Y still holds dQ^T of the previous step (of the previous item) until the read-out warps have it
+        if (q_iter > 0) mbar_wait(&dq_read, (q_iter - 1u) & 1u, ab);
+        tc_fence_after();
+        issue_kk(TM_Y, v_base, do_base + st * TILE_BYTES);
+        umma_commit(&dpt_full);
+      }
+      for (int s = 0; s < n_steps; ++s, ++q_iter) {
+        const uint32_t st = q_iter & 1u;
+        const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
+        const bool has_next = (s + 1 < n_steps);
+        mbar_wait(&p_ready, q_iter & 1u, ab);
+        tc_fence_after();
+        issue_dv(TM_X, do_base + st * TILE_BYTES, s > 0);
+        umma_commit(&dv_done);       // the dO tile of this stage may now be overwritten with dS^T
+        if (has_next) {
+          mbar_wait(&q_full[st_n], ph_n, ab);
+          tc_fence_after();
+          issue_kk(TM_X, k_base, q_base + st_n * TILE_BYTES);
+          umma_commit(&st_full);
+        }
+        mbar_wait(&ds_ready, q_iter & 1u, ab);
+        tc_fence_after();
+        issue_dq(do_base + st * TILE_BYTES);
+        umma_commit(&dq_full);
+        issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
+        umma_commit(&qdo_empty[st]);
+        // every product that reads K / V has been issued: the next item's tiles may come in
+        if (!has_next) umma_commit(&kv_free);
+        if (has_next) {
+          mbar_wait(&do_full[st_n], ph_n, ab);
+          mbar_wait(&dq_read, q_iter & 1u, ab);
+          tc_fence_after();
+          issue_kk(TM_Y, v_base, do_base + st_n * TILE_BYTES);
+          umma_commit(&dpt_full);
+        }
+      }
+      umma_commit(&acc_done);
+      ring_release(ring, n_ring);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// dq[token of row r] = bf16(scale * dq_acc[r]) for the rows the selection lists (every row when
+// q_idx is null). One warp per row, four floats per lane and head.
+__global__ void __launch_bounds__(256)
+    bwd_dq_finish_kernel(const float* __restrict__ dq_acc, const int64_t* __restrict__ q_idx,
+                         const int32_t* __restrict__ sq_ptr, __nv_bfloat16* __restrict__ dq, int n_tokens, int hq,
+                         float scale, int* status) {
+  const int sq = q_idx ? min(max(__ldg(sq_ptr), 0), n_tokens) : n_tokens;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < sq; r += warps) {
+    long long tok = q_idx ? __ldg(q_idx + r) : (long long)r;
+    if (tok < 0 || tok >= n_tokens) {
+      if (lane == 0 && status) atomicCAS(status, 0, (int)DEV_BAD_INDEX);
+      continue;
+    }
+    const float4* src = reinterpret_cast<const float4*>(dq_acc + (size_t)r * hq * HEAD_DIM) + lane;
+    uint2* dst = reinterpret_cast<uint2*>(dq + (size_t)tok * hq * HEAD_DIM) + lane;
+    for (int h = 0; h < hq; ++h) {
+      const float4 v = __ldcs(src + h * 32);
+      dst[h * 32] = make_uint2(pack_bf16x2(v.x * scale, v.y * scale), pack_bf16x2(v.z * scale, v.w * scale));
+    }
+  }
+}
+
+int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, const CUtensorMap& tm_k,
+                          const CUtensorMap& tm_v, const BwdArgs& a, float* dq_acc, const int32_t* sq_ptr,
+                          cudaStream_t stream) {
+  static thread_local int attr_set_dev = -1;
+  int dev = 0;
+  LOGO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (attr_set_dev != dev) {
+    LOGO_CHECK_CUDA(
+        cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+    attr_set_dev = dev;
+  }
+  const int sms = sm_count();
+  LOGO_CHECK_CUDA(cudaMemsetAsync(a.counter_dkv, 0, sizeof(int), stream));
+  prof_begin(PROF_BWD_FUSED, stream);
+  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a, dq_acc);
+  prof_end(PROF_BWD_FUSED, stream);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  prof_begin(PROF_BWD_FINISH, stream);
+  bwd_dq_finish_kernel<<<sms * 8, 256, 0, stream>>>(dq_acc, a.q_idx, sq_ptr, a.dq, a.n_tokens, a.hq, a.scale, a.status);
+  prof_end(PROF_BWD_FINISH, stream);
+  LOGO_CHECK_CUDA(cudaGetLastError());
+  return LOGO_OK;
+}
+
+}  // namespace logo

@@ -24,7 +24,6 @@ struct AttnArgs {
   // backward only
   const __nv_bfloat16* d_o;  // [n_tokens, hq, 128]
   float* delta;              // [n_tokens, hq]  sum_d o * do
-  float* dq_acc;             // unused by the two-kernel backward
   __nv_bfloat16* dq;         // [n_tokens, hq, 128]
   __nv_bfloat16* dk;         // [n_tokens, h, 128]
   __nv_bfloat16* dv;         // [n_tokens, h, 128]

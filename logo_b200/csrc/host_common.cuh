@@ -44,7 +44,10 @@ int launch_zero_unselected_rows(void* base, const int64_t* q_idx, const int32_t*
                                 size_t row_bytes, cudaStream_t stream);
 
 // Per-kernel event timing (see logo_profile_enable): kernels report under these indices.
-enum ProfKind { PROF_SELECT = 0, PROF_ATTN_FWD = 1, PROF_BWD_PRE = 2, PROF_BWD_DKV = 3, PROF_BWD_DQ = 4, PROF_KINDS = 5 };
+enum ProfKind {
+  PROF_SELECT = 0, PROF_ATTN_FWD = 1, PROF_BWD_PRE = 2, PROF_BWD_DKV = 3, PROF_BWD_DQ = 4, PROF_BWD_FUSED = 5,
+  PROF_BWD_FINISH = 6, PROF_KINDS = 7
+};
 bool prof_enabled();
 void prof_begin(int kind, cudaStream_t stream);
 void prof_end(int kind, cudaStream_t stream);

@@ -71,18 +71,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-#ifdef LOGO_MBAR_TEST_WAIT
-  // build-time alternative: non-blocking test (pure polling), for latency experiments
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -92,7 +80,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity), "r"(LOGO_TRYWAIT_HINT_NS)
       : "memory");
-#endif
   return ok != 0;
 }
 
@@ -108,6 +95,7 @@ __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
 struct AbortState {
   volatile int* smem_abort;  // CTA-wide flag in shared memory
   int* gmem_status;          // status word in global memory (may be null)
+  uint64_t timeout_ns;       // limit of one wait; 0 = LOGO_WAIT_TIMEOUT_NS
 };
 
 // Bounded wait. Returns false if the CTA is (or becomes) aborted. The clock is only consulted
@@ -125,7 +113,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > LOGO_WAIT_TIMEOUT_NS) {
+      } else if (now - t0 > (ab.timeout_ns ? ab.timeout_ns : LOGO_WAIT_TIMEOUT_NS)) {
         *ab.smem_abort = 1;
         if (ab.gmem_status) atomicCAS(ab.gmem_status, 0, (int)DEV_WAIT_TIMEOUT);
         return false;
@@ -277,7 +265,8 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 //           every part of A lies inside the fp32 columns it was computed from, so the warps that
 //           produce the parts never touch each other's columns.
 //   K_BEGIN, K_END: the k-steps to issue (default all eight); `accumulate_first` applies to K_BEGIN.
-template <bool A_TMEM, bool B_MN, int A_SPLIT = 0, int K_BEGIN = 0, int K_END = 8>
+//   A_MN  : A comes from shared memory MN-major ([k][m] rows as they lie in memory, 2 KB per k-step).
+template <bool A_TMEM, bool B_MN, int A_SPLIT = 0, int K_BEGIN = 0, int K_END = 8, bool A_MN = false>
 __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
                                                uint32_t accumulate_first) {
   if (elect_one()) {
@@ -306,7 +295,7 @@ __device__ __forceinline__ void umma_tile_k128(uint32_t d_tmem, uint64_t a0, uin
             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
             "}\n"
             :
-            : "r"(d_tmem), "l"(a0 + (uint64_t)kmaj), "l"(b), "r"(idesc), "r"(acc)
+            : "r"(d_tmem), "l"(a0 + (A_MN ? (uint64_t)kk * 128u : (uint64_t)kmaj)), "l"(b), "r"(idesc), "r"(acc)
             : "memory");
       }
     }

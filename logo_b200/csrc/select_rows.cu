@@ -153,7 +153,10 @@ __global__ void __launch_bounds__(SEL_THREADS)
         }
         const bool ready = (st >> 32) != 0;
         if (!__all_sync(0xffffffffu, ready)) {
-          if (globaltimer_ns() - t0 > LOGO_WAIT_TIMEOUT_NS) {
+          // the lanes read the clock independently: the verdict must be the same in all of them, or some
+          // would leave the loop while the rest wait in the full-mask vote above
+          const bool expired = __any_sync(0xffffffffu, globaltimer_ns() - t0 > LOGO_WAIT_TIMEOUT_NS);
+          if (expired) {
             if (lane == 0 && status) atomicCAS(status, 0, (int)DEV_SCAN_TIMEOUT);
             break;
           }
@@ -309,13 +312,15 @@ extern "C" size_t logo_select_workspace_bytes(int n_tokens) {
   return logo::SEL_WS_HEADER + (size_t)nb * (sizeof(unsigned long long) + sizeof(float)) + 16;
 }
 
-extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
-                                const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
-                                int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta, float* gate_sum, void* workspace, size_t workspace_bytes, int32_t* status,
-                                logo_stream_t stream_) {
-  using namespace logo;
-  cudaStream_t stream = (cudaStream_t)stream_;
-  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+namespace logo {
+
+// Argument checks and the two launches shared by logo_select_rows and logo_select_rows_static;
+// `scratch` holds logo_select_workspace_bytes(n_tokens) bytes, whoever owns them. It is cleared on the
+// stream first: the ticket and the look-back words must start at zero.
+static int select_rows_impl(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
+                            const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
+                            int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta, float* gate_sum, void* scratch,
+                            int32_t* status, cudaStream_t stream) {
   LOGO_REQUIRE(cu_seqlens && cu_seqlens_q && tile_off && meta, LOGO_ERR_INVALID,
                "cu_seqlens, cu_seqlens_q, tile_off and meta must not be NULL");
   LOGO_REQUIRE(n_tokens == 0 || (gate && q_idx && pos_ids), LOGO_ERR_INVALID,
@@ -327,19 +332,14 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
     LOGO_REQUIRE(thres_dtype >= LOGO_DTYPE_BF16 && thres_dtype <= LOGO_DTYPE_F16, LOGO_ERR_INVALID,
                  "unknown threshold dtype %d", thres_dtype);
   }
-  LOGO_REQUIRE(workspace && workspace_bytes >= logo_select_workspace_bytes(n_tokens), LOGO_ERR_WORKSPACE,
-               "select workspace too small: need %zu bytes", logo_select_workspace_bytes(n_tokens));
-  LOGO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15u) == 0, LOGO_ERR_INVALID,
-               "select workspace must be 16-byte aligned");
-
   const int nblocks = sel_num_blocks(n_tokens);
-  LOGO_CHECK_CUDA(cudaMemsetAsync(workspace, 0, logo_select_workspace_bytes(n_tokens), stream));
+  LOGO_CHECK_CUDA(cudaMemsetAsync(scratch, 0, logo_select_workspace_bytes(n_tokens), stream));
   prof_begin(PROF_SELECT, stream);
   if (nblocks > 0) {
 #define LOGO_LAUNCH_SELECT(T, ISB)                                                                        \
   select_kernel<T, ISB><<<nblocks, SEL_THREADS, 0, stream>>>(static_cast<const T*>(gate), thres, thres_dtype, \
                                                              cu_seqlens, n_seq, n_tokens, q_idx, pos_ids,  \
-                                                             workspace, nblocks, status)
+                                                             scratch, nblocks, status)
     switch (gate_dtype) {
       case LOGO_DTYPE_BF16: LOGO_LAUNCH_SELECT(__nv_bfloat16, false); break;
       case LOGO_DTYPE_F16: LOGO_LAUNCH_SELECT(__half, false); break;
@@ -350,10 +350,26 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
     LOGO_CHECK_CUDA(cudaGetLastError());
   }
   finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum,
-                                          workspace, nblocks, status);
+                                          scratch, nblocks, status);
   prof_end(PROF_SELECT, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;
+}
+
+}  // namespace logo
+
+extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* thres, int thres_dtype,
+                                const int32_t* cu_seqlens, int n_seq, int n_tokens, int64_t* q_idx, int32_t* pos_ids,
+                                int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta, float* gate_sum,
+                                void* workspace, size_t workspace_bytes, int32_t* status, logo_stream_t stream_) {
+  using namespace logo;
+  LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
+  LOGO_REQUIRE(workspace && workspace_bytes >= logo_select_workspace_bytes(n_tokens), LOGO_ERR_WORKSPACE,
+               "select workspace too small: need %zu bytes", logo_select_workspace_bytes(n_tokens));
+  LOGO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15u) == 0, LOGO_ERR_INVALID,
+               "select workspace must be 16-byte aligned");
+  return select_rows_impl(gate, gate_dtype, thres, thres_dtype, cu_seqlens, n_seq, n_tokens, q_idx, pos_ids,
+                          cu_seqlens_q, tile_off, meta, gate_sum, workspace, status, (cudaStream_t)stream_);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -368,7 +384,9 @@ extern "C" int logo_select_rows(const void* gate, int gate_dtype, const void* th
 //
 // `g_select_scratch` is a device symbol: inside host code the name is only a stand-in, not
 // an address a kernel could use. The device address is looked up with cudaGetSymbolAddress,
-// once per device with that device current, and cached; kernels receive that pointer.
+// once per device with that device current, and cached; kernels receive that pointer. The cached
+// address does not survive cudaDeviceReset: a process that resets a device must not call this
+// entry point on it afterwards.
 // ---------------------------------------------------------------------------------------
 namespace logo {
 
@@ -406,46 +424,15 @@ extern "C" int logo_select_rows_static(const void* gate, int gate_dtype, const v
                                        int32_t* pos_ids, int32_t* cu_seqlens_q, int32_t* tile_off, int32_t* meta,
                                        float* gate_sum, int32_t* status, logo_stream_t stream_) {
   using namespace logo;
-  cudaStream_t stream = (cudaStream_t)stream_;
   LOGO_REQUIRE(n_tokens >= 0 && n_seq >= 0, LOGO_ERR_INVALID, "n_tokens and n_seq must be non-negative");
   LOGO_REQUIRE(n_tokens <= SELECT_STATIC_MAX_TOKENS, LOGO_ERR_UNSUPPORTED,
                "logo_select_rows_static handles at most %d tokens per call (got %d); use logo_select_rows with a "
                "caller workspace for larger inputs",
                SELECT_STATIC_MAX_TOKENS, n_tokens);
-  LOGO_REQUIRE(cu_seqlens && cu_seqlens_q && tile_off && meta, LOGO_ERR_INVALID,
-               "cu_seqlens, cu_seqlens_q, tile_off and meta must not be NULL");
-  LOGO_REQUIRE(n_tokens == 0 || (gate && q_idx && pos_ids), LOGO_ERR_INVALID,
-               "gate, q_idx and pos_ids must not be NULL");
-  LOGO_REQUIRE(gate_dtype >= LOGO_DTYPE_BF16 && gate_dtype <= LOGO_DTYPE_BOOL, LOGO_ERR_INVALID,
-               "unknown gate dtype %d", gate_dtype);
-  if (gate_dtype != LOGO_DTYPE_BOOL) {
-    LOGO_REQUIRE(thres != nullptr, LOGO_ERR_INVALID, "thres must not be NULL for a floating-point gate");
-    LOGO_REQUIRE(thres_dtype >= LOGO_DTYPE_BF16 && thres_dtype <= LOGO_DTYPE_F16, LOGO_ERR_INVALID,
-                 "unknown threshold dtype %d", thres_dtype);
-  }
   void* scratch = nullptr;
-  int rc = select_static_scratch(&scratch);
+  const int rc = select_static_scratch(&scratch);
   if (rc) return rc;
-
-  const int nblocks = sel_num_blocks(n_tokens);
-  // The array keeps what the previous call left: the ticket and the look-back words must start at zero.
-  LOGO_CHECK_CUDA(cudaMemsetAsync(scratch, 0, logo_select_workspace_bytes(n_tokens), stream));
-  if (nblocks > 0) {
-#define LOGO_LAUNCH_SELECT_STATIC(T, ISB)                                                                  \
-  select_kernel<T, ISB><<<nblocks, SEL_THREADS, 0, stream>>>(static_cast<const T*>(gate), thres, thres_dtype, \
-                                                             cu_seqlens, n_seq, n_tokens, q_idx, pos_ids,  \
-                                                             scratch, nblocks, status)
-    switch (gate_dtype) {
-      case LOGO_DTYPE_BF16: LOGO_LAUNCH_SELECT_STATIC(__nv_bfloat16, false); break;
-      case LOGO_DTYPE_F16: LOGO_LAUNCH_SELECT_STATIC(__half, false); break;
-      case LOGO_DTYPE_F32: LOGO_LAUNCH_SELECT_STATIC(float, false); break;
-      default: LOGO_LAUNCH_SELECT_STATIC(uint8_t, true); break;
-    }
-#undef LOGO_LAUNCH_SELECT_STATIC
-    LOGO_CHECK_CUDA(cudaGetLastError());
-  }
-  finalize_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, n_seq, n_tokens, q_idx, cu_seqlens_q, tile_off, meta, gate_sum,
-                                          scratch, nblocks, status);
-  LOGO_CHECK_CUDA(cudaGetLastError());
-  return LOGO_OK;
+  // The array keeps what the previous call left; select_rows_impl clears the part this call uses.
+  return select_rows_impl(gate, gate_dtype, thres, thres_dtype, cu_seqlens, n_seq, n_tokens, q_idx, pos_ids,
+                          cu_seqlens_q, tile_off, meta, gate_sum, scratch, status, (cudaStream_t)stream_);
 }

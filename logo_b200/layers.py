@@ -25,10 +25,17 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
+import os
+
 from . import _lib, ops
 from .cache import Cache
 
-__all__ = ["Attention", "LoGoAttention", "RMSNorm", "RotaryEmbedding", "apply_rotary_pos_emb", "rotate_half"]
+# LOGO_B200_CHECK_STATUS=1: every layer call reads the device status word afterwards (this
+# synchronises) and raises if a kernel reported a problem. Off by default: the layers never sync.
+_CHECK_STATUS = os.environ.get("LOGO_B200_CHECK_STATUS", "0") not in ("", "0")
+
+__all__ = ["Attention", "LoGoAttention", "RMSNorm", "RotaryEmbedding", "apply_rotary_pos_emb", "check_status",
+           "rotate_half"]
 
 
 class RMSNorm(nn.Module):
@@ -78,9 +85,15 @@ class RotaryEmbedding(nn.Module):
         dim = self.config.hidden_size // self.config.num_attention_heads
         return 1.0 / (self.config.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float().to(device) / dim))
 
+    # `module.to(torch.bfloat16)` also casts the `inv_freq` buffer, which costs the rotation angle about
+    # three decimal digits at position ~500. By default the tables are built from an fp32 copy. The
+    # reference uses the cast buffer as it is (logo/modules/rotary.py:66-71): set this to True to
+    # reproduce the angles a checkpoint saw if it was trained through a bf16-cast reference model.
+    use_cast_inv_freq = False
+
     def _inv_freq_for(self, device) -> torch.Tensor:
-        # `module.to(torch.bfloat16)` also casts the `inv_freq` buffer, which costs the rotation angle
-        # about three decimal digits at position ~500; the tables are always built from an fp32 copy.
+        if self.use_cast_inv_freq:
+            return self.inv_freq.float()
         if self.inv_freq.dtype == torch.float32 and self.inv_freq.device == device:
             return self.inv_freq
         key = str(device)
@@ -236,8 +249,9 @@ class LoGoAttention(nn.Module):
             cos, sin = position_embeddings
         # rotary embedding of both branches (logo/layers/logo.py:136-139): one kernel per tensor
         n_tok = bsz * q_len
-        cos2 = cos.reshape(n_tok, D).to(torch.bfloat16)
-        sin2 = sin.reshape(n_tok, D).to(torch.bfloat16)
+        # tables may come with a broadcast batch of 1 (the reference multiplies with broadcasting)
+        cos2 = cos.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
+        sin2 = sin.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
         q_l = ops.rope(q_l.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
         k_l = ops.rope(k_l.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
         q_g = ops.rope(q_g.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
@@ -256,30 +270,42 @@ class LoGoAttention(nn.Module):
                 raise TypeError("decode needs a logo_b200.Cache")
             st = past_key_value.append(self.layer_idx, k_l, v_l, k_g, v_g, self.local_window_size, layout="bthd")
             local, glob = decode_attention(q_l.reshape(bsz, H, D), q_g.reshape(bsz, H, D), st, gate_flat, thres, scale)
+            self._last_status = st.status
             fused = ops.fuse_norm_blend(local, glob, gate_flat, thres, w_l, w_g, eps, self.use_context_norm)
         else:
+            filled = 0
             if past_key_value is not None:
                 if not isinstance(past_key_value, Cache):
                     raise TypeError("the cache must be a logo_b200.Cache")
                 filled = (past_key_value.layers[self.layer_idx].length
                           if len(past_key_value.layers) > self.layer_idx else 0)
-                if filled != 0:
-                    raise NotImplementedError("multi-token steps on a non-empty cache are not implemented")
-                past_key_value.append(self.layer_idx, k_l, v_l, k_g, v_g, self.local_window_size, layout="bthd")
             n = bsz * q_len
-            if cu_seqlens is not None:
-                cu = cu_seqlens
-            else:  # equal-length batch packed to one varlen batch (logo.py:200-209)
-                cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
-            sel = ops.select_rows(gate_flat, thres, cu)
-            local = ops.SWAFunction.apply(q_l.reshape(n, H, D), k_l.reshape(n, HKV, D), v_l.reshape(n, HKV, D),
-                                          self.local_window_size, scale, sel)
-            glob = ops.SQFullAttentionFunction.apply(q_g.reshape(1, n, H, D), k_g.reshape(1, n, HKV, D),
-                                                     v_g.reshape(1, n, HKV, D), scale, sel).view(n, H, D)
+            if filled != 0:
+                # several new tokens on top of cached ones (chunked prefill, logo/cache.py:95-118)
+                if cu_seqlens is not None:
+                    raise NotImplementedError("a packed batch cannot continue a cache: pass [B, T] inputs")
+                local, glob, sel = _continue_with_cache(past_key_value, self.layer_idx, q_l, k_l, v_l, q_g, k_g, v_g,
+                                                        gate_flat, thres, self.local_window_size, scale)
+            else:
+                if past_key_value is not None:
+                    past_key_value.append(self.layer_idx, k_l, v_l, k_g, v_g, self.local_window_size, layout="bthd")
+                if cu_seqlens is not None:
+                    cu = cu_seqlens
+                else:  # equal-length batch packed to one varlen batch (logo.py:200-209)
+                    cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
+                sel = ops.select_rows(gate_flat, thres, cu)
+                local = ops.SWAFunction.apply(q_l.reshape(n, H, D), k_l.reshape(n, HKV, D), v_l.reshape(n, HKV, D),
+                                              self.local_window_size, scale, sel)
+                glob = ops.SQFullAttentionFunction.apply(q_g.reshape(1, n, H, D), k_g.reshape(1, n, HKV, D),
+                                                         v_g.reshape(1, n, HKV, D), scale, sel).view(n, H, D)
+            self._last_status = sel.status
             fused = ops.fuse_norm_blend(local, glob, gate_flat, thres, w_l, w_g, eps, self.use_context_norm)
             if self.training:   # logo.py:251-255, from the select kernel's by-products (no sync)
                 with torch.no_grad():
-                    self.gate_avg.add_(sel.gate_sum.to(self.gate_avg.dtype))
+                    if filled != 0:   # the continuation's selection also lists (never selected) cached rows
+                        self.gate_avg.add_(gate.sum().to(self.gate_avg.dtype))
+                    else:
+                        self.gate_avg.add_(sel.gate_sum.to(self.gate_avg.dtype))
                     self.global_token_count.add_(sel.meta[0].to(self.global_token_count.dtype))
                     self.total_token_count.add_(gate.numel())
 
@@ -289,9 +315,84 @@ class LoGoAttention(nn.Module):
                 self.global_token_count.add_((gate >= thres).sum().to(self.global_token_count.dtype))
                 self.total_token_count.add_(gate.numel())
 
+        if _CHECK_STATUS:
+            ops.check_device_status(self._last_status, f"LoGoAttention layer {self.layer_idx}")
         attn_output = self.o_proj(fused.view(bsz, q_len, H * D))
         attn_output = self.resid_dropout(attn_output)
         return attn_output, None, past_key_value
+
+
+def _continue_with_cache(cache, layer_idx, q_l, k_l, v_l, q_g, k_g, v_g, gate_flat, thres, window, scale):
+    """Both branches for ``t`` new tokens per sequence on top of ``T0`` cached ones (inference only).
+
+    The reference concatenates the cached states with the new ones and lets flash-attn align the
+    causal mask to the bottom right (logo/cache.py:95-118, logo/layers/logo.py:141-179). Here the
+    cached keys / values are laid out token-major in front of the new ones, each sequence becomes one
+    packed sequence of ``T0 + t`` (global) or ``min(T0, window) + t`` (local) tokens whose leading
+    rows carry no query, and the ordinary kernels run: the select kernel is given a gate of -inf
+    for the cached rows, so the global branch computes the new selected rows only.
+    Inputs are ``[B, t, H, D]`` (rotary embedding applied); returns ``(local, glob, sel)`` with
+    ``local``, ``glob`` ``[B * t, H, D]``.
+    """
+    if torch.is_grad_enabled() and any(x.requires_grad for x in (q_l, k_l, v_l, q_g, k_g, v_g)):
+        raise NotImplementedError("continuing a cache with several tokens is an inference path (run it under no_grad)")
+    bsz, t, H, D = q_l.shape
+    st = cache.layers[layer_idx]
+    T0 = st.length
+    w0 = min(T0, window)
+    dev = q_l.device
+    with torch.no_grad():
+        if window > 0:
+            old_kl, old_vl = cache._local_window(st, T0, window)              # [B, HKV, w0, D]
+        cache.append(layer_idx, k_l, v_l, k_g, v_g, window, layout="bthd")
+        st = cache.layers[layer_idx]
+
+        def packed(old_bhtd, new_bthd):                                      # -> [B * (t_old + t), heads, D]
+            return torch.cat([old_bhtd.transpose(1, 2), new_bthd], dim=1).reshape(-1, new_bthd.shape[2], D)
+
+        # local branch: the last w0 cached tokens + the new ones, every row computed, cached rows dropped
+        local = None
+        if window > 0:          # (the dense layer has no local branch and passes window 0)
+            zq = torch.zeros(bsz, w0, H, D, dtype=q_l.dtype, device=dev)
+            ql = torch.cat([zq, q_l], dim=1).reshape(-1, H, D)
+            kl, vl = packed(old_kl, k_l), packed(old_vl, v_l)
+            cu_l = torch.arange(0, (bsz + 1) * (w0 + t), w0 + t, dtype=torch.int32, device=dev)
+            sel_l = ops.select_rows(torch.ones(ql.shape[0], dtype=torch.bool, device=dev), None, cu_l)
+            lo, _ = ops.swa_fwd_raw(ql, kl, vl, sel_l, window, scale)
+            local = lo.view(bsz, w0 + t, H, D)[:, w0:].reshape(bsz * t, H, D)
+
+        # global branch: the whole cache (it already holds the new tokens) token-major
+        kg = st.k_full[:, :, : T0 + t].transpose(1, 2).reshape(-1, st.k_full.shape[1], D)
+        vg = st.v_full[:, :, : T0 + t].transpose(1, 2).reshape(-1, st.v_full.shape[1], D)
+        zq = torch.zeros(bsz, T0, H, D, dtype=q_g.dtype, device=dev)
+        qg = torch.cat([zq, q_g], dim=1).reshape(-1, H, D)
+        gate_ext = torch.full((bsz, T0 + t), float("-inf"), dtype=gate_flat.dtype, device=dev)
+        gate_ext[:, T0:] = gate_flat.view(bsz, t)
+        cu_g = torch.arange(0, (bsz + 1) * (T0 + t), T0 + t, dtype=torch.int32, device=dev)
+        sel = ops.select_rows(gate_ext.reshape(-1), thres, cu_g)
+        go, _ = ops.sq_attn_fwd_raw(qg, kg, vg, sel, scale, zero_fill=True)
+        glob = go.view(bsz, T0 + t, H, D)[:, T0:].reshape(bsz * t, H, D)
+    return local, glob, sel
+
+
+def check_status(obj) -> None:
+    """Raises if a kernel launched on behalf of ``obj`` left an error in its device status word.
+
+    ``obj`` is a module tree holding LoGo layers (the status of each layer's most recent call is
+    looked at) or a :class:`logo_b200.Cache`. The layers themselves never read the word, because
+    reading it synchronises the host with the device; call this at a point where a sync is
+    acceptable (end of a step, after generation), or set ``LOGO_B200_CHECK_STATUS=1`` to check after
+    every layer call while debugging.
+    """
+    if isinstance(obj, Cache):
+        for i, st in enumerate(obj.layers):
+            if st.status is not None:
+                ops.check_device_status(st.status, f"cache layer {i}")
+        return
+    for name, mod in obj.named_modules():
+        status = getattr(mod, "_last_status", None)
+        if status is not None:
+            ops.check_device_status(status, f"layer {name or type(mod).__name__}")
 
 
 def decode_attention(q_local, q_global, st, gate_flat, thres, scale: float):
@@ -312,12 +413,13 @@ def decode_attention(q_local, q_global, st, gate_flat, thres, scale: float):
     thres = thres.reshape(-1)[:1].contiguous()
     ws_bytes = lib.logo_decode_workspace_bytes(b, hq, st.length)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    rc = lib.logo_decode_attn(q_local.data_ptr(), q_global.data_ptr(), st.k_ring.data_ptr(), st.v_ring.data_ptr(),
-                              st.ring, st.k_full.data_ptr(), st.v_full.data_ptr(), st.t_max, ctx.data_ptr(),
-                              gate_flat.data_ptr(), _lib.torch_dtype_code(gate_flat.dtype), thres.data_ptr(),
-                              _lib.torch_dtype_code(thres.dtype), o_local.data_ptr(), o_global.data_ptr(), b, hq, h,
-                              d, st.length, float(scale), ws.data_ptr(), ws.numel(), st.status.data_ptr(),
-                              _lib.current_stream_ptr(dev))
+    with _lib.on_device(q_local):
+        rc = lib.logo_decode_attn(q_local.data_ptr(), q_global.data_ptr(), st.k_ring.data_ptr(), st.v_ring.data_ptr(),
+                                  st.ring, st.k_full.data_ptr(), st.v_full.data_ptr(), st.t_max, ctx.data_ptr(),
+                                  gate_flat.data_ptr(), _lib.torch_dtype_code(gate_flat.dtype), thres.data_ptr(),
+                                  _lib.torch_dtype_code(thres.dtype), o_local.data_ptr(), o_global.data_ptr(), b, hq,
+                                  h, d, st.length, float(scale), ws.data_ptr(), ws.numel(), st.status.data_ptr(),
+                                  _lib.current_stream_ptr(dev))
     _lib.check(rc, "logo_decode_attn")
     return o_local, o_global
 
@@ -391,8 +493,9 @@ class Attention(nn.Module):
         else:
             cos, sin = position_embeddings
         n_tok = bsz * q_len
-        cos2 = cos.reshape(n_tok, D).to(torch.bfloat16)
-        sin2 = sin.reshape(n_tok, D).to(torch.bfloat16)
+        # tables may come with a broadcast batch of 1 (the reference multiplies with broadcasting)
+        cos2 = cos.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
+        sin2 = sin.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
         q = ops.rope(query_states.view(n_tok, H, D), cos2, sin2)          # [N, H, D]
         k = ops.rope(key_states.view(n_tok, HKV, D), cos2, sin2)
         scale = D ** -0.5
@@ -410,20 +513,31 @@ class Attention(nn.Module):
             _, out = decode_attention(qd, qd, st, ones, zero, scale)
             out = out.view(bsz, 1, H * D)
         else:
+            filled = 0
             if past_key_value is not None:
                 if not isinstance(past_key_value, Cache):
                     raise TypeError("the cache must be a logo_b200.Cache")
                 filled = (past_key_value.layers[self.layer_idx].length
                           if len(past_key_value.layers) > self.layer_idx else 0)
-                if filled != 0:
-                    raise NotImplementedError("multi-token steps on a non-empty cache are not implemented")
-                kb = k.view(bsz, q_len, HKV, D)
-                past_key_value.append(self.layer_idx, kb, v, kb, v, 0, layout="bthd")
-            if cu_seqlens is not None:
-                cu = cu_seqlens
+            if filled != 0:
+                if cu_seqlens is not None:
+                    raise NotImplementedError("a packed batch cannot continue a cache: pass [B, T] inputs")
+                # several new tokens on top of cached ones: the global-branch route of the LoGo layer
+                # with every new row selected
+                qb, kb = q.view(bsz, q_len, H, D), k.view(bsz, q_len, HKV, D)
+                ones = torch.ones(bsz * q_len, dtype=torch.bfloat16, device=q.device)
+                zero = torch.zeros(1, dtype=torch.float32, device=q.device)
+                _, out, _ = _continue_with_cache(past_key_value, self.layer_idx, qb, kb, v, qb, kb, v, ones, zero, 0, scale)
+                out = out.view(bsz, q_len, H * D)
             else:
-                cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
-            out = ops.swa_attn(q, k, v.reshape(n_tok, HKV, D), cu, self._FULL_WINDOW, scale).view(bsz, q_len, H * D)
+                if past_key_value is not None:
+                    kb = k.view(bsz, q_len, HKV, D)
+                    past_key_value.append(self.layer_idx, kb, v, kb, v, 0, layout="bthd")
+                if cu_seqlens is not None:
+                    cu = cu_seqlens
+                else:
+                    cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
+                out = ops.swa_attn(q, k, v.reshape(n_tok, HKV, D), cu, self._FULL_WINDOW, scale).view(bsz, q_len, H * D)
 
         attn_output = self.o_proj(out)
         attn_output = self.resid_dropout(attn_output)

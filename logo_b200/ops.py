@@ -35,7 +35,8 @@ HEAD_DIM = 128
 
 
 # ----------------------------------------------------------------------------------------
-# error metrics (logo/ops/common.py:24-41)
+# error metrics: the reference's public helpers, restated from logo/ops/common.py:24-41 (same
+# names, arguments and formulas, so that checks written against `logo.ops` read the same here)
 # ----------------------------------------------------------------------------------------
 def get_abs_err(x, y):
     return (x.detach() - y.detach()).flatten().abs().max().item()
@@ -132,10 +133,11 @@ def select_rows(gate_or_mask: torch.Tensor, thres: Optional[torch.Tensor], cu_se
             raise ValueError("a floating-point gate needs a threshold tensor")
         thres = thres.reshape(-1)[:1].contiguous()
         thres_ptr, thres_code = thres.data_ptr(), _lib.torch_dtype_code(thres.dtype)
-    rc = lib.logo_select_rows(flat.data_ptr(), _lib.torch_dtype_code(flat.dtype), thres_ptr, thres_code,
-                              cu.data_ptr(), nseq, n, q_idx.data_ptr(), pos_ids.data_ptr(), cu_q.data_ptr(),
-                              tile_off.data_ptr(), meta.data_ptr(), gate_sum.data_ptr(), ws.data_ptr(), ws_bytes,
-                              status.data_ptr(), _lib.current_stream_ptr(dev))
+    with _lib.on_device(flat):
+        rc = lib.logo_select_rows(flat.data_ptr(), _lib.torch_dtype_code(flat.dtype), thres_ptr, thres_code,
+                                  cu.data_ptr(), nseq, n, q_idx.data_ptr(), pos_ids.data_ptr(), cu_q.data_ptr(),
+                                  tile_off.data_ptr(), meta.data_ptr(), gate_sum.data_ptr(), ws.data_ptr(), ws_bytes,
+                                  status.data_ptr(), _lib.current_stream_ptr(dev))
     _lib.check(rc, "logo_select_rows")
     return SelMeta(q_idx, pos_ids, cu_q, cu, tile_off, meta, gate_sum, status, n, nseq)
 
@@ -172,10 +174,11 @@ def sq_attn_fwd_raw(q, k, v, m: SelMeta, scale: float, zero_fill: bool = True):
     h = k.shape[1]
     o = torch.empty_like(q)
     lse = torch.empty(n, hq, dtype=torch.float32, device=q.device)
-    rc = lib.logo_sq_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                              m.q_idx.data_ptr(), m.pos_ids.data_ptr(), m.cu_seqlens_q.data_ptr(),
-                              m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h,
-                              d, float(scale), int(zero_fill), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
+    with _lib.on_device(q):
+        rc = lib.logo_sq_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                  m.q_idx.data_ptr(), m.pos_ids.data_ptr(), m.cu_seqlens_q.data_ptr(),
+                                  m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h,
+                                  d, float(scale), int(zero_fill), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
     _lib.check(rc, "logo_sq_attn_fwd")
     return o, lse
 
@@ -188,9 +191,10 @@ def swa_fwd_raw(q, k, v, m: SelMeta, window: int, scale: float):
     h = k.shape[1]
     o = torch.empty_like(q)
     lse = torch.empty(n, hq, dtype=torch.float32, device=q.device)
-    rc = lib.logo_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                          m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h, d,
-                          int(window), float(scale), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
+    with _lib.on_device(q):
+        rc = lib.logo_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                              m.cu_seqlens_k.data_ptr(), m.tile_off.data_ptr(), m.meta.data_ptr(), m.n_seq, n, hq, h, d,
+                              int(window), float(scale), m.status.data_ptr(), _lib.current_stream_ptr(q.device))
     _lib.check(rc, "logo_swa_fwd")
     return o, lse
 
@@ -198,10 +202,20 @@ def swa_fwd_raw(q, k, v, m: SelMeta, window: int, scale: float):
 # ----------------------------------------------------------------------------------------
 # autograd functions
 # ----------------------------------------------------------------------------------------
+# Autocast bookkeeping of the reference's autograd function (logo/ops/triton_utils.py:42-44,
+# logo/ops/selected_full_attn.py:450-452,473-474): inside a torch.autocast region floating-point
+# inputs are cast to bf16 (the only dtype the kernels take) and the body runs with autocast off;
+# the backward runs in the autocast state of its forward. Outside autocast nothing is cast.
+_fwd_bf16 = torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+_fwd_plain = torch.amp.custom_fwd(device_type="cuda")
+_bwd = torch.amp.custom_bwd(device_type="cuda")
+
+
 class SQFullAttentionFunction(torch.autograd.Function):
     """Counterpart of logo/ops/selected_full_attn.py:449-492 (same argument order)."""
 
     @staticmethod
+    @_fwd_bf16
     def forward(ctx, q, k, v, scale, sel: SelMeta):
         B, T, HQ, K = q.shape
         H, V = v.shape[2], v.shape[3]
@@ -216,6 +230,7 @@ class SQFullAttentionFunction(torch.autograd.Function):
         return o.view(B, T, HQ, V)
 
     @staticmethod
+    @_bwd
     def backward(ctx, do):
         from .ops_bwd import sq_attn_bwd_raw
 
@@ -230,6 +245,7 @@ class SWAFunction(torch.autograd.Function):
     """Local sliding-window branch (the flash-attn call of logo/layers/logo.py:166-179)."""
 
     @staticmethod
+    @_fwd_bf16
     def forward(ctx, q, k, v, window, scale, sel: SelMeta):
         qf, kf, vf = q.contiguous(), k.contiguous(), v.contiguous()
         o, lse = swa_fwd_raw(qf, kf, vf, sel, window, scale)
@@ -238,6 +254,7 @@ class SWAFunction(torch.autograd.Function):
         return o
 
     @staticmethod
+    @_bwd
     def backward(ctx, do):
         from .ops_bwd import swa_bwd_raw
 
@@ -335,8 +352,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
         raise ValueError("rmsnorm: weight must have the size of the last dimension")
     xc = x.contiguous()
     out = torch.empty_like(xc)
-    rc = lib.logo_rmsnorm_fwd(xc.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), xc.numel() // dim, dim,
-                              float(eps), _lib.current_stream_ptr(x.device))
+    with _lib.on_device(xc):
+        rc = lib.logo_rmsnorm_fwd(xc.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), xc.numel() // dim, dim,
+                                  float(eps), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "logo_rmsnorm_fwd")
     return out
 
@@ -358,8 +376,9 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if u2.stride(1) != 1 or u2.stride(0) % 8 or u2.data_ptr() % 16:
         u2 = u2.contiguous()
     out = torch.empty(gate.shape, dtype=torch.bfloat16, device=gate.device)
-    rc = lib.logo_silu_mul(g2.data_ptr(), g2.stride(0), u2.data_ptr(), u2.stride(0), out.data_ptr(), g2.shape[0], dim,
-                           _lib.current_stream_ptr(gate.device))
+    with _lib.on_device(g2):
+        rc = lib.logo_silu_mul(g2.data_ptr(), g2.stride(0), u2.data_ptr(), u2.stride(0), out.data_ptr(), g2.shape[0], dim,
+                               _lib.current_stream_ptr(gate.device))
     _lib.check(rc, "logo_silu_mul")
     return out
 
@@ -373,8 +392,9 @@ def _rope_call(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: b
     if x.stride(2) != 1 or x.stride(0) % 8 or x.stride(1) % 8 or x.data_ptr() % 16:
         x = x.contiguous()      # rows must be contiguous and 16-byte aligned; any token / head strides are fine
     out = torch.empty((n, h, d), dtype=x.dtype, device=x.device)
-    rc = lib.logo_rope(x.data_ptr(), x.stride(0), x.stride(1), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, h, d,
-                       int(inverse), _lib.current_stream_ptr(x.device))
+    with _lib.on_device(x):
+        rc = lib.logo_rope(x.data_ptr(), x.stride(0), x.stride(1), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, h, d,
+                           int(inverse), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "logo_rope")
     return out
 
@@ -383,6 +403,7 @@ class RopeFunction(torch.autograd.Function):
     """``(x * cos) + (rotate_half(x) * sin)`` on packed ``[N, H, 128]`` bf16 rows, one kernel each way."""
 
     @staticmethod
+    @_fwd_bf16
     def forward(ctx, x, cos, sin):
         _require_cuda(x, cos, sin)
         if x.dtype != torch.bfloat16 or cos.dtype != torch.bfloat16 or sin.dtype != torch.bfloat16:
@@ -394,6 +415,7 @@ class RopeFunction(torch.autograd.Function):
         return _rope_call(x, cos, sin, False)
 
     @staticmethod
+    @_bwd
     def backward(ctx, d_out):
         cos, sin = ctx.saved_tensors
         return _rope_call(d_out, cos, sin, True), None, None
@@ -411,6 +433,7 @@ class FuseFunction(torch.autograd.Function):
     """out[N, H*D] = (1-g) * RMSNorm_l(local) + g * RMSNorm_g(glob), g = gate masked below thres."""
 
     @staticmethod
+    @_fwd_plain      # no cast: the threshold and the norm weights keep their own precision
     def forward(ctx, local, glob, gate, thres, w_local, w_global, eps, use_norm):
         lib = _lib.load()
         _require_cuda(local, glob, gate, thres)
@@ -428,11 +451,12 @@ class FuseFunction(torch.autograd.Function):
         else:
             w_code = _lib.DTYPE_BF16
         out = torch.empty(n, h * d, dtype=torch.bfloat16, device=local.device)
-        rc = lib.logo_fuse_fwd(local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(), _lib.DTYPE_BF16,
-                               thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
-                               _lib.ptr(w_local) if use_norm else None, _lib.ptr(w_global) if use_norm else None,
-                               w_code, out.data_ptr(), n, h, d, float(eps), int(bool(use_norm)),
-                               _lib.current_stream_ptr(local.device))
+        with _lib.on_device(local):
+            rc = lib.logo_fuse_fwd(local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(), _lib.DTYPE_BF16,
+                                   thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
+                                   _lib.ptr(w_local) if use_norm else None, _lib.ptr(w_global) if use_norm else None,
+                                   w_code, out.data_ptr(), n, h, d, float(eps), int(bool(use_norm)),
+                                   _lib.current_stream_ptr(local.device))
         _lib.check(rc, "logo_fuse_fwd")
         ctx.save_for_backward(local, glob, gate_flat, thres, w_local if use_norm else None,
                               w_global if use_norm else None)
@@ -440,6 +464,7 @@ class FuseFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @_bwd
     def backward(ctx, d_out):
         lib = _lib.load()
         local, glob, gate_flat, thres, w_local, w_global = ctx.saved_tensors
@@ -451,11 +476,12 @@ class FuseFunction(torch.autograd.Function):
         d_wg = torch.empty_like(w_global) if ctx.use_norm else None
         ws_bytes = lib.logo_fuse_bwd_workspace_bytes(n)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=local.device)
-        rc = lib.logo_fuse_bwd(d_out.data_ptr(), local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(),
-                               _lib.DTYPE_BF16, thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
-                               _lib.ptr(w_local), _lib.ptr(w_global), ctx.w_code, d_local.data_ptr(),
-                               d_glob.data_ptr(), d_gate.data_ptr(), _lib.ptr(d_wl), _lib.ptr(d_wg), n, h, d, ctx.eps,
-                               int(ctx.use_norm), ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(local.device))
+        with _lib.on_device(local):
+            rc = lib.logo_fuse_bwd(d_out.data_ptr(), local.data_ptr(), glob.data_ptr(), gate_flat.data_ptr(),
+                                   _lib.DTYPE_BF16, thres.data_ptr(), _lib.torch_dtype_code(thres.dtype),
+                                   _lib.ptr(w_local), _lib.ptr(w_global), ctx.w_code, d_local.data_ptr(),
+                                   d_glob.data_ptr(), d_gate.data_ptr(), _lib.ptr(d_wl), _lib.ptr(d_wg), n, h, d, ctx.eps,
+                                   int(ctx.use_norm), ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(local.device))
         _lib.check(rc, "logo_fuse_bwd")
         return d_local, d_glob, d_gate.view(ctx.gate_shape), None, d_wl, d_wg, None, None
 

@@ -1,6 +1,7 @@
 """Training-time controller of the global-attention budget.
 
-Same entry point and behaviour as the reference's ``logo/update.py:17-75``: layers are found by
+This is host logic whose contract is its body: it is the reference's function
+(``logo/update.py:17-75``) restated, not a new design. Same entry point and behaviour: layers are found by
 their four buffers (``gate_thres``, ``gate_avg``, ``global_token_count``,
 ``total_token_count``), the observed global ratio moves each threshold by a signed step, and
 the counters are cleared. The two all-reduces of ``update.py:52-54`` are issued as one
