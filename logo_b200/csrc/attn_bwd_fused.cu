@@ -19,8 +19,12 @@
 // Tensor memory is full (X, Y, dK, dV = 512 columns): dQ^T shares Y with dP^T, so the next
 // dP^T waits until the read-out warps hold the previous dQ^T in registers.
 //
-// Warp roles (448 threads): 0-7 element-wise (lane quarter w % 4, 64 query columns each),
-// 8-11 dQ read-out (one per lane quarter), 12 TMA producer + work claiming, 13 MMA issue.
+// Warp roles (512 threads = four warpgroups): 0-7 element-wise (lane quarter w % 4, 64 query
+// columns each), 8-11 dQ read-out (one per lane quarter), 12 TMA producer + work claiming, 13 MMA
+// issue, 14-15 idle. The kernel starts with 128 registers per thread; the element-wise warpgroups
+// raise their share to 168 with setmaxnreg (they keep a 64-column fp32 P row and a dP chunk live),
+// the read-out warpgroup drops to 120 and the last one to 56: every scheduler holds one warp of each
+// warpgroup, 168 + 168 + 120 + 56 = 512 registers per lane = its whole register file.
 //
 // The order in which key tiles reach a dQ row is not fixed, so dQ can differ between runs in
 // the last bit of its fp32 sum (dK and dV are accumulated in a fixed order and are reproducible).
@@ -30,15 +34,17 @@ namespace logo {
 
 constexpr int FUSED_EW_WARPS = 8;
 constexpr int FUSED_DQ_WARPS = 4;
-constexpr int FUSED_THREADS = (FUSED_EW_WARPS + FUSED_DQ_WARPS + 2) * 32;
+constexpr int FUSED_THREADS = 512;
+
+__device__ __forceinline__ void reg_inc_168() { asm volatile("setmaxnreg.inc.sync.aligned.u32 168;"); }
+__device__ __forceinline__ void reg_dec_120() { asm volatile("setmaxnreg.dec.sync.aligned.u32 120;"); }
+__device__ __forceinline__ void reg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
-// 448 threads x 144 registers = 63 K of the 64 K register file (a launch bound of 448 threads alone
-// makes the compiler budget for 512 and stop at 128 registers, which spills)
-__global__ void __maxnreg__(144)
+__global__ void __launch_bounds__(FUSED_THREADS, 1)
     attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           const BwdArgs a, float* __restrict__ dq_acc) {
@@ -100,6 +106,7 @@ __global__ void __maxnreg__(144)
 
   if (warp < FUSED_EW_WARPS) {
     // ================= element-wise warps =================
+    reg_inc_168();
     const int quad = warp & 3, half = warp >> 2;
     const int row = quad * 32 + lane;   // key inside the tile
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -281,7 +288,8 @@ __global__ void __maxnreg__(144)
   } else if (warp < FUSED_EW_WARPS + FUSED_DQ_WARPS) {
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
-    // and the 128 query rows of the step as columns.
+    // and the 128 query rows of the step as columns, read in two batches of 64.
+    reg_dec_120();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const size_t row_stride = (size_t)a.hq * HEAD_DIM;   // floats between consecutive query rows of dq_acc
@@ -302,33 +310,43 @@ __global__ void __maxnreg__(144)
           float* base = dq_acc + ((size_t)(it.bos_q + i * TILE) * a.hq + hq) * HEAD_DIM + quad * 32 + lane;
           const bool ok = mbar_wait(&dq_full, idx & 1u, ab);
           tc_fence_after();
-          uint32_t r0[32], r1[32], r2[32], r3[32];
-          tmem_ld32(TM_Y + lane_off, r0);
-          tmem_ld32(TM_Y + lane_off + 32u, r1);
-          tmem_ld32(TM_Y + lane_off + 64u, r2);
-          tmem_ld32(TM_Y + lane_off + 96u, r3);
-          tmem_ld_wait();
-          tc_fence_before();
-          mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
-          if (ok) {
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld32(TM_Y + lane_off, r0);
+            tmem_ld32(TM_Y + lane_off + 32u, r1);
+            tmem_ld_wait();
+            if (ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) red_add_f32(base + (size_t)j * row_stride, __uint_as_float(r0[j]));
+              for (int j = 0; j < 32; ++j)
+                if (j < nvalid) red_add_f32(base + (size_t)j * row_stride, __uint_as_float(r0[j]));
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (32 + j < nvalid) red_add_f32(base + (size_t)(32 + j) * row_stride, __uint_as_float(r1[j]));
+              for (int j = 0; j < 32; ++j)
+                if (32 + j < nvalid) red_add_f32(base + (size_t)(32 + j) * row_stride, __uint_as_float(r1[j]));
+            }
+          }
+          {
+            uint32_t r2[32], r3[32];
+            tmem_ld32(TM_Y + lane_off + 64u, r2);
+            tmem_ld32(TM_Y + lane_off + 96u, r3);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
+            if (ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (64 + j < nvalid) red_add_f32(base + (size_t)(64 + j) * row_stride, __uint_as_float(r2[j]));
+              for (int j = 0; j < 32; ++j)
+                if (64 + j < nvalid) red_add_f32(base + (size_t)(64 + j) * row_stride, __uint_as_float(r2[j]));
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (96 + j < nvalid) red_add_f32(base + (size_t)(96 + j) * row_stride, __uint_as_float(r3[j]));
+              for (int j = 0; j < 32; ++j)
+                if (96 + j < nvalid) red_add_f32(base + (size_t)(96 + j) * row_stride, __uint_as_float(r3[j]));
+            }
           }
         }
       }
       ring_release(ring, n_ring);
     }
-  } else if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS) {
+  } else {
+   reg_dec_56();
+   if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS) {
     // ================= producer: claims and decodes items, issues the TMA loads =================
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
@@ -387,7 +405,7 @@ __global__ void __maxnreg__(144)
         }
       }
     }
-  } else {
+   } else if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS + 1) {
     // ================= MMA issuer: the whole warp walks this code, an elected lane issues =================
     const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // S^T, dP^T: both operands K-major
     const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // dV, dK: B operand MN-major
@@ -470,6 +488,7 @@ __global__ void __maxnreg__(144)
       umma_commit(&acc_done);
       ring_release(ring, n_ring);
     }
+   }
   }
 
   tc_fence_before();

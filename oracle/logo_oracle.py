@@ -278,6 +278,26 @@ def logo_layer_ref(
     return out
 
 
+def dense_attention_layer_ref(hidden: torch.Tensor, weights: Dict[str, torch.Tensor], cu_seqlens: Sequence[int],
+                              num_heads: int, num_kv_heads: int, rope_theta: float = 10000.0) -> torch.Tensor:
+    """logo/layers/attn.py:54-121 (the dense causal layer of non-LoGo decoder layers), no cache, no dropout:
+    projections, rotary embedding, full causal attention within each packed sequence, output projection.
+    hidden [N, hidden] packed tokens; returns [N, hidden]."""
+    n, hid = hidden.shape
+    d = hid // num_heads
+    cu = [int(x) for x in cu_seqlens]
+    q = (hidden @ weights["q_proj.weight"].T).view(n, num_heads, d)        # :68-70
+    k = (hidden @ weights["k_proj.weight"].T).view(n, num_kv_heads, d)
+    v = (hidden @ weights["v_proj.weight"].T).view(n, num_kv_heads, d)
+    cu_t = torch.as_tensor(cu)
+    idx = torch.arange(n)
+    pos = idx - cu_t[torch.searchsorted(cu_t, idx, right=True) - 1]
+    cos, sin = rope_cos_sin(pos, d, rope_theta, hidden.dtype)             # :76-80
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    o, _ = attention_dense_ref(q, k, v, cu, None, None, None)             # :102-114 (flash-attn, causal)
+    return o.reshape(n, hid) @ weights["o_proj.weight"].T                 # :116-119
+
+
 # ---------------------------------------------------------------------------------------
 # decode step and the cache contract
 # ---------------------------------------------------------------------------------------

@@ -68,7 +68,31 @@ LAYER_CASES = {
                          batch=1, seqlen=420, lens=[100, 0, 320], seed=101),
     "small_batch": dict(hidden=256, heads=2, kv_heads=1, window=128, gate_thres=0.5, backend="flash",
                         batch=2, seqlen=200, lens=None, seed=102),
+    # global_qk_param='scale_offset' (logo/layers/logo.py:44-51,80-84), GQA, an empty sequence
+    "scale_offset_varlen": dict(hidden=256, heads=2, kv_heads=1, window=128, gate_thres=0.5, backend="triton",
+                                batch=1, seqlen=450, lens=[180, 0, 270], seed=103, param="scale_offset"),
 }
+
+# the dense causal layer used for attn_type_list != 0 (logo/layers/attn.py:22-121)
+DENSE_ATTN_CASE = dict(hidden=512, heads=4, kv_heads=2, batch=2, seqlen=300, seed=104)
+
+
+def dense_attn_weights(case=DENSE_ATTN_CASE):
+    rs = np.random.RandomState(case["seed"])
+    hid, nh, nkv = case["hidden"], case["heads"], case["kv_heads"]
+    d = hid // nh
+    return {"q_proj.weight": (0.05 * rs.standard_normal((nh * d, hid))).astype(np.float32),
+            "k_proj.weight": (0.05 * rs.standard_normal((nkv * d, hid))).astype(np.float32),
+            "v_proj.weight": (0.05 * rs.standard_normal((nkv * d, hid))).astype(np.float32),
+            "o_proj.weight": (0.05 * rs.standard_normal((hid, hid))).astype(np.float32)}
+
+
+def dense_attn_inputs(case=DENSE_ATTN_CASE):
+    rs = np.random.RandomState(case["seed"] + 1000)
+    b, t = case["batch"], case["seqlen"]
+    hidden = rs.standard_normal((b, t, case["hidden"])).astype(np.float32)
+    pos = np.broadcast_to(np.arange(t, dtype=np.int64)[None], (b, t)).copy()
+    return hidden, pos
 
 
 def layer_weights(case):
@@ -83,10 +107,15 @@ def layer_weights(case):
     w["v_proj.weight"] = (0.02 * rs.standard_normal((nkv * d, hid))).astype(np.float32)
     w["o_proj.weight"] = (0.02 * rs.standard_normal((hid, hid))).astype(np.float32)
     w["gate_proj.weight"] = (0.02 * rs.standard_normal((1, hid))).astype(np.float32)
-    eye = np.eye(d, dtype=np.float32)
-    w["q_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nh, d, d))).astype(np.float32)
-    w["k_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
-    w["v_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
+    if case.get("param", "linear_proj") == "scale_offset":
+        for name, heads in (("q", nh), ("k", nkv), ("v", nkv)):
+            w[f"{name}_global_scale"] = (1 + 0.1 * rs.standard_normal(heads * d)).astype(np.float32)
+            w[f"{name}_global_offset"] = (0.1 * rs.standard_normal(heads * d)).astype(np.float32)
+    else:
+        eye = np.eye(d, dtype=np.float32)
+        w["q_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nh, d, d))).astype(np.float32)
+        w["k_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
+        w["v_global_proj"] = (eye[None] + 0.02 * rs.standard_normal((nkv, d, d))).astype(np.float32)
     w["context_norm_local.weight"] = (1 + 0.1 * rs.standard_normal(d)).astype(np.float32)
     w["context_norm_global.weight"] = (1 + 0.1 * rs.standard_normal(d)).astype(np.float32)
     return w

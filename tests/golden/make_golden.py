@@ -37,7 +37,7 @@ sys.path.insert(0, REF)
 sys.path.insert(0, str(OUT))
 
 from golden_inputs import (attn_case_inputs, layer_case_inputs, selection_cases, layer_weights,  # noqa: E402
-                           ATTN_CASES, LAYER_CASES)
+                           dense_attn_inputs, dense_attn_weights, ATTN_CASES, DENSE_ATTN_CASE, LAYER_CASES)
 
 
 @triton.jit
@@ -93,6 +93,9 @@ def install_shims():
         return o.squeeze(0) if cu_seqlens is not None else o
 
     ll.flash_attention_forward = dense_flash
+    import logo.layers.attn as la
+
+    la.flash_attention_forward = dense_flash     # the dense layer calls the same wrapper (attn.py:102)
 
 
 def gen_selection():
@@ -133,7 +136,7 @@ def build_ref_layer(case):
     from logo.layers.logo import LoGoAttention
     cfg = LoGoConfig(hidden_size=case["hidden"], num_attention_heads=case["heads"],
                      num_key_value_heads=case["kv_heads"], window_size=case["window"],
-                     global_qk_param="linear_proj", gate_thres_init=case["gate_thres"],
+                     global_qk_param=case.get("param", "linear_proj"), gate_thres_init=case["gate_thres"],
                      sparse_full_attn_backend=case["backend"], num_hidden_layers=1, rms_norm_eps=1e-5)
     layer = LoGoAttention(cfg, layer_idx=0)
     w = layer_weights(case)
@@ -165,6 +168,21 @@ def gen_layer():
             out[f"{name}/out"] = y
         out[f"{name}/gate"] = gate.numpy().reshape(-1)
         print(name, "selected", int(sel.sum()), "of", sel.numel())
+
+    # the dense causal layer (logo/layers/attn.py), with the same stand-in for the flash-attn wheel
+    from logo.configuration_logo import LoGoConfig
+    from logo.layers.attn import Attention
+    case = DENSE_ATTN_CASE
+    cfg = LoGoConfig(hidden_size=case["hidden"], num_attention_heads=case["heads"],
+                     num_key_value_heads=case["kv_heads"], num_hidden_layers=1)
+    layer = Attention(cfg, layer_idx=0).eval()
+    with torch.no_grad():
+        for name, arr in dense_attn_weights(case).items():
+            dict(layer.named_parameters())[name].copy_(torch.from_numpy(arr))
+        hidden, pos = dense_attn_inputs(case)
+        y, _, _ = layer(torch.from_numpy(hidden), position_ids=torch.from_numpy(pos))
+    out["dense_attn/out"] = y.numpy()
+    print("dense_attn out std", float(y.std()))
     np.savez_compressed(OUT / "layer.npz", **out)
 
 
@@ -200,6 +218,21 @@ def gen_decode():
     out["decode/seen"] = np.array([cache.get_seq_length(0)])
     print("decode: local", tuple(st["attn_state"][0].shape), "full", tuple(st["attn_state_full"][0].shape),
           "max |cached - full|", float(np.abs(out["decode/step_out"] - out["decode/full_out"][:, T0:]).max()))
+
+    # several tokens on top of a non-empty cache (logo/cache.py:95-118): prefill 100, a chunk of 50
+    # (the local branch then sees 100 cached + 50 new keys and uses its window), one more token
+    cache2 = Cache()
+    with torch.no_grad():
+        T1, chunk = 100, 50
+        layer(h[:, :T1], position_ids=torch.arange(T1)[None].expand(B, -1), past_key_value=cache2, use_cache=True)
+        y_chunk, _, _ = layer(h[:, T1:T1 + chunk], position_ids=torch.arange(T1, T1 + chunk)[None].expand(B, -1),
+                              past_key_value=cache2, use_cache=True)
+        y_last, _, _ = layer(h[:, T1 + chunk:T1 + chunk + 1], position_ids=torch.full((B, 1), T1 + chunk),
+                             past_key_value=cache2, use_cache=True)
+    out["decode/chunk_out"] = y_chunk.numpy()
+    out["decode/after_chunk_out"] = y_last.numpy()
+    print("chunk: max |chunked - full|", float(np.abs(out["decode/chunk_out"] - out["decode/full_out"][:, T1:T1 + chunk]).max()),
+          "then one token", float(np.abs(out["decode/after_chunk_out"] - out["decode/full_out"][:, T1 + chunk:T1 + chunk + 1]).max()))
     np.savez_compressed(OUT / "decode.npz", **out)
 
 

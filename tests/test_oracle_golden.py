@@ -3,8 +3,8 @@ import numpy as np
 import pytest
 import torch
 
-from golden_inputs import (ATTN_CASES, LAYER_CASES, attn_case_inputs, layer_case_inputs, layer_weights,
-                           selection_cases)
+from golden_inputs import (ATTN_CASES, DENSE_ATTN_CASE, LAYER_CASES, attn_case_inputs, dense_attn_inputs,
+                           dense_attn_weights, layer_case_inputs, layer_weights, selection_cases)
 from oracle import logo_oracle as orc
 
 
@@ -58,6 +58,35 @@ def test_layer_matches_reference_layer(golden, name):
         assert abs(out.astype(np.float64).sum() - g[f"{name}/out_sum"][0]) < 1e-2
     else:
         np.testing.assert_allclose(out, g[f"{name}/out"], atol=2e-5)
+
+
+def test_dense_attention_layer_matches_reference_layer(golden):
+    """The oracle's restatement of the dense causal layer against the reference's Attention module."""
+    case = DENSE_ATTN_CASE
+    hidden, _ = dense_attn_inputs(case)
+    w = {k: torch.from_numpy(v) for k, v in dense_attn_weights(case).items()}
+    b, t, hid = hidden.shape
+    out = orc.dense_attention_layer_ref(torch.from_numpy(hidden).reshape(b * t, hid), w, list(range(0, (b + 1) * t, t)),
+                                        case["heads"], case["kv_heads"])
+    np.testing.assert_allclose(out.reshape(b, t, hid).numpy(), golden["layer"]["dense_attn/out"], atol=2e-5)
+
+
+def test_chunk_on_a_filled_cache_equals_the_rows_of_the_full_forward(golden):
+    """The reference layer fed 50 new tokens on top of 100 cached ones returns the rows 100..149 of its
+    own uncached forward (and the following single token row 150): what a continuation has to
+    reproduce is therefore the oracle layer on the whole sequence, restricted to the new rows."""
+    g = golden["decode"]
+    case = LAYER_CASES["small_batch"]
+    w = {k: torch.from_numpy(v) for k, v in layer_weights(case).items()}
+    B, T = 2, 156
+    hidden = torch.from_numpy(np.random.RandomState(4242).standard_normal((B, T, case["hidden"])).astype(np.float32))
+    np.testing.assert_allclose(g["decode/chunk_out"], g["decode/full_out"][:, 100:150], atol=2e-6)
+    np.testing.assert_allclose(g["decode/after_chunk_out"], g["decode/full_out"][:, 150:151], atol=2e-6)
+    for b in range(B):
+        out = orc.logo_layer_ref(hidden[b, :151], w, [0, 151], case["heads"], case["kv_heads"], case["window"],
+                                 case["gate_thres"], 1e-5)
+        np.testing.assert_allclose(out[100:150].numpy(), g["decode/chunk_out"][b], atol=2e-5)
+        np.testing.assert_allclose(out[150:151].numpy(), g["decode/after_chunk_out"][b], atol=2e-5)
 
 
 def test_decode_and_cache_match_reference(golden):
