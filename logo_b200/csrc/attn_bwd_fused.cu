@@ -13,18 +13,22 @@
 //     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
 //     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
 // dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
-// dedicated warps and added to an fp32 accumulator in global memory with red.global.add
-// (32 lanes = 32 consecutive floats of one query row: one 128-byte reduction per instruction);
-// bwd_dq_finish_kernel scales, converts and scatters it to the token rows afterwards.
+// dedicated warps, laid down as an fp32 [query][head dim] tile in the shared memory of the step's
+// Q and dS^T tiles (dK was their last reader) and added to an fp32 accumulator in global memory
+// by two bulk tensor reductions (cp.reduce.async.bulk: the reduction runs in L2 on whole lines;
+// per-thread red.global.add was measured 5x slower, bound by the SM's atomic issue rate). The
+// stage goes back to the TMA producer once the reductions have read it. bwd_dq_finish_kernel
+// scales, converts and scatters the accumulator to the token rows afterwards.
 // Tensor memory is full (X, Y, dK, dV = 512 columns): dQ^T shares Y with dP^T, so the next
 // dP^T waits until the read-out warps hold the previous dQ^T in registers.
 //
 // Warp roles (512 threads = four warpgroups): 0-7 element-wise (lane quarter w % 4, 64 query
 // columns each), 8-11 dQ read-out (one per lane quarter), 12 TMA producer + work claiming, 13 MMA
 // issue, 14-15 idle. The kernel starts with 128 registers per thread; the element-wise warpgroups
-// raise their share to 168 with setmaxnreg (they keep a 64-column fp32 P row and a dP chunk live),
-// the read-out warpgroup drops to 120 and the last one to 56: every scheduler holds one warp of each
-// warpgroup, 168 + 168 + 120 + 56 = 512 registers per lane = its whole register file.
+// raise their share to 160 with setmaxnreg (they keep a 64-column fp32 P row and a dP chunk live),
+// the read-out warpgroup takes 144 (a whole 128-column row of dQ^T in registers, so that Y is released
+// after one round of loads) and the last one drops to 48: every scheduler holds one warp of each
+// warpgroup, 160 + 160 + 144 + 48 = 512 registers per lane = its whole register file.
 //
 // The order in which key tiles reach a dQ row is not fixed, so dQ can differ between runs in
 // the last bit of its fp32 sum (dK and dV are accumulated in a fixed order and are reproducible).
@@ -36,18 +40,14 @@ constexpr int FUSED_EW_WARPS = 8;
 constexpr int FUSED_DQ_WARPS = 4;
 constexpr int FUSED_THREADS = 512;
 
-__device__ __forceinline__ void reg_inc_168() { asm volatile("setmaxnreg.inc.sync.aligned.u32 168;"); }
-__device__ __forceinline__ void reg_dec_120() { asm volatile("setmaxnreg.dec.sync.aligned.u32 120;"); }
-__device__ __forceinline__ void reg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
-
-__device__ __forceinline__ void red_add_f32(float* addr, float v) {
-  asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
-}
+__device__ __forceinline__ void reg_inc_ew() { asm volatile("setmaxnreg.inc.sync.aligned.u32 160;"); }
+__device__ __forceinline__ void reg_dec_dq() { asm volatile("setmaxnreg.inc.sync.aligned.u32 144;"); }
+__device__ __forceinline__ void reg_dec_misc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 48;"); }
 
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
     attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                          const BwdArgs a, float* __restrict__ dq_acc) {
+                          const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages; stage s & 1 holds dS^T of step s once dV(s) is done
 
   __shared__ uint64_t kv_full, kv_free, q_full[2], do_full[2], qdo_empty[2];
-  __shared__ uint64_t st_full, dpt_full, p_ready, dv_done, ds_ready, dq_full, dq_read, acc_done;
+  __shared__ uint64_t st_full, dpt_full, p_ready, dv_done, ds_ready, dq_full, dk_done, dq_read, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ __align__(16) float s_lse[2][TILE];
@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     mbar_init(&dv_done, 1);
     mbar_init(&ds_ready, FUSED_EW_WARPS);
     mbar_init(&dq_full, 1);
+    mbar_init(&dk_done, 1);
     mbar_init(&dq_read, FUSED_DQ_WARPS);
     mbar_init(&acc_done, 1);
     ring_init(ring, FUSED_EW_WARPS + FUSED_DQ_WARPS + 1);
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
 
   if (warp < FUSED_EW_WARPS) {
     // ================= element-wise warps =================
-    reg_inc_168();
+    reg_inc_ew();
     const int quad = warp & 3, half = warp >> 2;
     const int row = quad * 32 + lane;   // key inside the tile
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -288,11 +289,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   } else if (warp < FUSED_EW_WARPS + FUSED_DQ_WARPS) {
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
-    // and the 128 query rows of the step as columns, read in two batches of 64.
-    reg_dec_120();
+    // and the 128 query rows of the step as columns. The tile goes to shared memory transposed, as
+    // fp32 [query row][128]: rows 0-63 into the Q tile of the step's stage, rows 64-127 into its
+    // dO / dS^T tile (32 KB each), from where two bulk reductions add it to dq_acc.
+    reg_dec_dq();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const size_t row_stride = (size_t)a.hq * HEAD_DIM;   // floats between consecutive query rows of dq_acc
+    const bool issuer = (warp == FUSED_EW_WARPS) && (lane == 0);
     uint32_t idx = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
@@ -307,45 +310,50 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         for (int i = it.i0; i < it.i_end; ++i, ++idx) {
           const int hq = it.kvh * G + g;
           const int nvalid = min(it.nsel - i * TILE, TILE);
-          float* base = dq_acc + ((size_t)(it.bos_q + i * TILE) * a.hq + hq) * HEAD_DIM + quad * 32 + lane;
+          const uint32_t st = idx & 1u;
+          float* stage_lo = reinterpret_cast<float*>(sQ + st * TILE_BYTES) + quad * 32 + lane;    // query rows 0-63
+          float* stage_hi = reinterpret_cast<float*>(sDO + st * TILE_BYTES) + quad * 32 + lane;   // query rows 64-127
           const bool ok = mbar_wait(&dq_full, idx & 1u, ab);
           tc_fence_after();
-          {
-            uint32_t r0[32], r1[32];
-            tmem_ld32(TM_Y + lane_off, r0);
-            tmem_ld32(TM_Y + lane_off + 32u, r1);
-            tmem_ld_wait();
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tmem_ld32(TM_Y + lane_off, r0);
+          tmem_ld32(TM_Y + lane_off + 32u, r1);
+          tmem_ld32(TM_Y + lane_off + 64u, r2);
+          tmem_ld32(TM_Y + lane_off + 96u, r3);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
+          // dK of this step still reads the Q and dS^T tiles the staging overwrites
+          mbar_wait(&dk_done, idx & 1u, ab);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage_lo[j * HEAD_DIM] = __uint_as_float(r0[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage_lo[(32 + j) * HEAD_DIM] = __uint_as_float(r1[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage_hi[j * HEAD_DIM] = __uint_as_float(r2[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage_hi[(32 + j) * HEAD_DIM] = __uint_as_float(r3[j]);
+          fence_proxy_async_smem();
+          named_barrier_sync(4, FUSED_DQ_WARPS * 32);
+          if (issuer) {
+            // rows past the last valid query row of the tile hold exact zeros (their dS^T columns are
+            // zero); rows past the end of the accumulator are clipped by the tensor map
             if (ok) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nvalid) red_add_f32(base + (size_t)j * row_stride, __uint_as_float(r0[j]));
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (32 + j < nvalid) red_add_f32(base + (size_t)(32 + j) * row_stride, __uint_as_float(r1[j]));
+              const int x = hq * HEAD_DIM, y = it.bos_q + i * TILE;
+              tma_reduce_add_2d(&tm_dq, sQ + st * TILE_BYTES, x, y);
+              if (nvalid > 64) tma_reduce_add_2d(&tm_dq, sDO + st * TILE_BYTES, x, y + 64);
+              bulk_commit_group();
+              bulk_wait_read_all();
             }
-          }
-          {
-            uint32_t r2[32], r3[32];
-            tmem_ld32(TM_Y + lane_off + 64u, r2);
-            tmem_ld32(TM_Y + lane_off + 96u, r3);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
-            if (ok) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (64 + j < nvalid) red_add_f32(base + (size_t)(64 + j) * row_stride, __uint_as_float(r2[j]));
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (96 + j < nvalid) red_add_f32(base + (size_t)(96 + j) * row_stride, __uint_as_float(r3[j]));
-            }
+            mbar_arrive(&qdo_empty[st]);   // the stage may be refilled by the producer
           }
         }
       }
       ring_release(ring, n_ring);
     }
+    if (issuer) bulk_wait_all();
   } else {
-   reg_dec_56();
+   reg_dec_misc();
    if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS) {
     // ================= producer: claims and decodes items, issues the TMA loads =================
     if (lane == 0) {
@@ -386,7 +394,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           }
           const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
           const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
-          // the stage is free once dK and dQ^T of the step that used it (they read Q and dS^T) are done
+          // the stage is free once the dQ tile staged in it (after dK and dQ^T of its step) has been reduced
           mbar_wait(&qdo_empty[st], ph ^ 1u, ab);
           mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
           tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
@@ -474,7 +482,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         issue_dq(do_base + st * TILE_BYTES);
         umma_commit(&dq_full);
         issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
-        umma_commit(&qdo_empty[st]);
+        umma_commit(&dk_done);       // the read-out warps may now stage dQ over the Q and dS^T tiles
         // every product that reads K / V has been issued: the next item's tiles may come in
         if (!has_next) umma_commit(&kv_free);
         if (has_next) {
@@ -534,7 +542,12 @@ int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, con
   const int sms = sm_count();
   LOGO_CHECK_CUDA(cudaMemsetAsync(a.counter_dkv, 0, sizeof(int), stream));
   prof_begin(PROF_BWD_FUSED, stream);
-  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a, dq_acc);
+  CUtensorMap tm_dq;
+  const uint64_t acc_rows = a.q_idx ? (uint64_t)a.cap : (uint64_t)a.n_tokens;
+  const int rc = make_tmap_2d_f32(&tm_dq, dq_acc, (uint64_t)a.hq * HEAD_DIM, acc_rows, (uint64_t)a.hq * HEAD_DIM * 4,
+                                  HEAD_DIM, 64);
+  if (rc) return rc;
+  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, a);
   prof_end(PROF_BWD_FUSED, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_FINISH, stream);

@@ -50,6 +50,23 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return LOGO_OK;
 }
 
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                     uint32_t box_inner, uint32_t box_outer) {
+  std::call_once(g_encode_once, load_encode);
+  if (!g_encode) return set_error(LOGO_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  if (!aligned16(base) || (row_stride_bytes & 15u))
+    return set_error(LOGO_ERR_INVALID, "tensor base and row stride must be 16-byte aligned for TMA");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LOGO_ERR_CUDA, "cuTensorMapEncodeTiled (fp32) failed with CUresult %d", (int)r);
+  return LOGO_OK;
+}
+
 int sm_count() {
   static int cached[64];
   static std::mutex mu;

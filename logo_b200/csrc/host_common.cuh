@@ -33,6 +33,11 @@ int set_error(int code, const char* fmt, ...);
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
+// 2-D fp32 tensor map without swizzle (rows of `box_inner` floats lie contiguously in shared
+// memory): the destination of the bulk reductions that accumulate dQ.
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                     uint32_t box_inner, uint32_t box_outer);
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
