@@ -8,17 +8,16 @@
 //     dP^T = V dO^T           -> TMEM Y
 //     P^T  = exp2(S^T c - lse) masked, bf16       -> written into X (the A operand of dV)
 //     dV  += P^T dO                               (A from TMEM, B = dO tile read MN-major)
-//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory as a [key][query]
-//                                                    tile, into the dO stage dV has finished with
+//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory (tile X) as a
+//                                                    [key][query] tile
 //     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
 //     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
 // dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
-// dedicated warps, laid down as an fp32 [query][head dim] tile in the shared memory of the step's
-// Q and dS^T tiles (dK was their last reader) and added to an fp32 accumulator in global memory
-// by two bulk tensor reductions (cp.reduce.async.bulk: the reduction runs in L2 on whole lines;
-// per-thread red.global.add was measured 5x slower, bound by the SM's atomic issue rate). The
-// stage goes back to the TMA producer once the reductions have read it. bwd_dq_finish_kernel
-// scales, converts and scatters the accumulator to the token rows afterwards.
+// dedicated warps, laid down as an fp32 [query][head dim] tile in X (once dK has consumed dS^T),
+// 64 query rows at a time, and added to an fp32 accumulator in global memory by bulk tensor
+// reductions (cp.reduce.async.bulk: the reduction runs in L2 on whole lines; per-thread
+// red.global.add was measured 2.5x slower, bound by the SM's atomic issue rate).
+// bwd_dq_finish_kernel scales, converts and scatters the accumulator to the token rows afterwards.
 // Tensor memory is full (X, Y, dK, dV = 512 columns): dQ^T shares Y with dP^T, so the next
 // dP^T waits until the read-out warps hold the previous dQ^T in registers.
 //
@@ -44,31 +43,50 @@ __device__ __forceinline__ void reg_inc_ew() { asm volatile("setmaxnreg.inc.sync
 __device__ __forceinline__ void reg_dec_dq() { asm volatile("setmaxnreg.inc.sync.aligned.u32 144;"); }
 __device__ __forceinline__ void reg_dec_misc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 48;"); }
 
+// Shared memory (all of it dynamic, so that the 1024-byte alignment the swizzled tiles need costs no
+// padding): seven 32 KB tiles, then the per-step vectors, barriers and the work-item ring.
+struct FusedSmem {
+  static constexpr uint32_t K = 0, V = TILE_BYTES, Q = 2 * TILE_BYTES, DO = 4 * TILE_BYTES, X = 6 * TILE_BYTES;
+  static constexpr uint32_t LSE = 7 * TILE_BYTES, DELTA = LSE + TILE * 4, POS = DELTA + TILE * 4;
+  static constexpr uint32_t BARS = POS + TILE * 4;          // 8-byte aligned
+  static constexpr uint32_t N_BARS = 19 + 2 * ITEM_RING;
+  static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
+  static constexpr uint32_t MISC = ITEMS + ITEM_RING * ITEM_WORDS * 4;   // tmem slot, abort flag
+  static constexpr uint32_t BYTES = MISC + 16;
+};
+static_assert(FusedSmem::BYTES <= 232448, "the single-pass backward does not fit the 227 KB of shared memory");
+
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
     attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = smem + TILE_BYTES;
-  uint8_t* sQ = smem + 2 * TILE_BYTES;    // 2 stages
-  uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages; stage s & 1 holds dS^T of step s once dV(s) is done
-
-  __shared__ uint64_t kv_full, kv_free, q_full[2], do_full[2], qdo_empty[2];
-  __shared__ uint64_t st_full, dpt_full, p_ready, dv_done, ds_ready, dq_full, dk_done, dq_read, acc_done;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
-  __shared__ __align__(16) float s_lse[2][TILE];
-  __shared__ __align__(16) float s_delta[2][TILE];
-  __shared__ __align__(16) int s_pos[2][TILE];
-  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
-  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
-  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
-  const ItemRing ring{s_items, item_full, item_empty};
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem + FusedSmem::K;
+  uint8_t* sV = smem + FusedSmem::V;
+  uint8_t* sQ = smem + FusedSmem::Q;      // 2 stages
+  uint8_t* sDO = smem + FusedSmem::DO;    // 2 stages
+  // X: dS^T of the step ([key][query] bf16), then the two halves of its dQ tile ([query][128] fp32) on
+  // their way to the bulk reduction; at the end of an item the staging of the dK / dV stores
+  uint8_t* sX = smem + FusedSmem::X;
+  float* s_lse = reinterpret_cast<float*>(smem + FusedSmem::LSE);
+  float* s_delta = reinterpret_cast<float*>(smem + FusedSmem::DELTA);
+  int* s_pos = reinterpret_cast<int*>(smem + FusedSmem::POS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FusedSmem::BARS);
+  uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
+           *do_empty = bars + 8, &st_full = bars[10], &dpt_full = bars[11], &p_ready = bars[12], &ds_ready = bars[13],
+           &dq_full = bars[14], &dk_done = bars[15], &dq_read = bars[16], &x_free = bars[17], &acc_done = bars[18];
+  const ItemRing ring{reinterpret_cast<int*>(smem + FusedSmem::ITEMS), bars + 19, bars + 19 + ITEM_RING};
+  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + FusedSmem::MISC);
+  int& abort_flag = *reinterpret_cast<int*>(smem + FusedSmem::MISC + 4);
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
+
+  // the tile layouts (TMA 128-byte swizzle, UMMA descriptors) assume a 1024-byte aligned base
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (tid == 0 && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+    return;
+  }
 
   if (tid == 0) {
     abort_flag = 0;
@@ -76,17 +94,18 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     mbar_init(&kv_free, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
       mbar_init(&do_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+      mbar_init(&do_empty[s], 1);
     }
     mbar_init(&st_full, 1);
     mbar_init(&dpt_full, 1);
     mbar_init(&p_ready, FUSED_EW_WARPS);    // one arrival per warp
-    mbar_init(&dv_done, 1);
     mbar_init(&ds_ready, FUSED_EW_WARPS);
     mbar_init(&dq_full, 1);
     mbar_init(&dk_done, 1);
     mbar_init(&dq_read, FUSED_DQ_WARPS);
+    mbar_init(&x_free, 1);
     mbar_init(&acc_done, 1);
     ring_init(ring, FUSED_EW_WARPS + FUSED_DQ_WARPS + 1);
     fence_barrier_init();
@@ -115,22 +134,26 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const float c = a.scale_log2;
     uint32_t idx = 0, n_items = 0;
 
-    // lse / delta / pos of query tile `i` of head `hq`, loaded unconditionally from a clamped row
-    const int vrow = tid & (TILE - 1);
-    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) -> bool {
-      const int r = i * TILE + vrow;
+    // lse / delta / pos of row `tid` of query tile `i` of head `hq`: loaded unconditionally from a
+    // clamped row into registers (threads 0-127), stored to the shared vectors between two steps
+    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
+      const int r = i * TILE + (tid & (TILE - 1));
       const int rc = min(r, it.nsel - 1);
       const size_t sidx = (size_t)hq * a.cap + it.bos_q + rc;
       l = __ldg(a.lse_sel + sidx);
       d = __ldg(a.delta_sel + sidx);
       p = bwd_row_position(a, it.bos_q, rc);
-      return r < it.nsel;
+      if (r >= it.nsel) {   // rows past the end of the sequence see no key
+        l = 0.f;
+        d = 0.f;
+        p = -1;
+      }
     };
 
     uint32_t n_ring = 0;
     DkvItem it;
     long long w = ring_pop(ring, n_ring, it, ab);
-    bool vec_ready = false;   // the first-step vectors of `it` are already in s_*[idx & 1]
+    bool vec_ready = false;   // the first-step vectors of `it` are already in the shared vectors
     while (w >= 0) {
       DkvItem it_next;
       long long w_next = -1;
@@ -138,11 +161,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       const int nq = it.i_end - it.i0;
       const int key_pos = it.kv_start + row;
       const bool key_valid = key_pos < it.len_k;
-      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
-      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
       if (nq <= 0) {
         // no query can see this key tile: the gradients are zero
         if (key_valid) {
+          __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0;
+          __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             reinterpret_cast<uint4*>(dk_row)[g] = make_uint4(0, 0, 0, 0);
@@ -161,13 +184,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       const bool partial_keys = it.kv_start + TILE > it.len_k;
 
       if (!vec_ready) {
-        float l, d;
-        int p;
-        const bool ok = fetch_vec(it, it.kvh * G, it.i0, l, d, p);
         if (tid < TILE) {
-          s_lse[idx & 1u][tid] = ok ? l : 0.f;
-          s_delta[idx & 1u][tid] = ok ? d : 0.f;
-          s_pos[idx & 1u][tid] = ok ? p : -1;
+          float l, d;
+          int p;
+          fetch_vec(it, it.kvh * G, it.i0, l, d, p);
+          s_lse[tid] = l;
+          s_delta[tid] = d;
+          s_pos[tid] = p;
         }
         named_barrier_sync(3, 256);
       }
@@ -178,29 +201,20 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           i_nx = 0;
           ++g_nx;
         }
-        const uint32_t vb = idx & 1u;
-        // the vectors of the next step travel global -> shared asynchronously (the buffer they land
-        // in was last read before the named barrier of the previous step)
+        // the vectors of the next step (of the next item after the last step) start travelling now
         const bool has_next = (s + 1 < n_steps);
-        bool next_ok = true;
         if (!has_next) {
           w_next = ring_pop(ring, n_ring + 1, it_next, ab);
           vec_next = (w_next >= 0) && (it_next.i_end > it_next.i0);
         }
+        float l_nx = 0.f, d_nx = 0.f;
+        int p_nx = -1;
         if ((has_next || vec_next) && tid < TILE) {
-          const DkvItem& src = has_next ? it : it_next;
-          const int hq_nx = src.kvh * G + (has_next ? g_nx : 0);
-          const int r = (src.i0 + (has_next ? i_nx : 0)) * TILE + tid;
-          const int rc = min(r, src.nsel - 1);
-          next_ok = r < src.nsel;
-          const size_t sidx = (size_t)hq_nx * a.cap + src.bos_q + rc;
-          cp_async_4(&s_lse[vb ^ 1u][tid], a.lse_sel + sidx);
-          cp_async_4(&s_delta[vb ^ 1u][tid], a.delta_sel + sidx);
-          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + src.bos_q + rc);
-          else s_pos[vb ^ 1u][tid] = next_ok ? r : -1;
+          if (has_next) fetch_vec(it, it.kvh * G + g_nx, it.i0 + i_nx, l_nx, d_nx, p_nx);
+          else fetch_vec(it_next, it_next.kvh * G, it_next.i0, l_nx, d_nx, p_nx);
         }
 
-        const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
+        const int pos_first = s_pos[0], pos_last = s_pos[TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
                             (a.window > 0 && pos_last > it.kv_start + a.window);
         uint32_t p0[32], p1[32];
@@ -209,8 +223,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         tmem_ld32(TM_X + lane_off + (uint32_t)col0, p0);
         tmem_ld32(TM_X + lane_off + (uint32_t)col0 + 32, p1);
         tmem_ld_wait();
-        prob_chunk_col(p0, c, &s_lse[vb][col0], &s_pos[vb][col0], masked, key_valid, key_pos, a.window);
-        prob_chunk_col(p1, c, &s_lse[vb][col0 + 32], &s_pos[vb][col0 + 32], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p0, c, &s_lse[col0], &s_pos[col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p1, c, &s_lse[col0 + 32], &s_pos[col0 + 32], masked, key_valid, key_pos, a.window);
         {
           uint32_t pk[32];
           pack_chunk(p0, pk);
@@ -228,25 +242,20 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           uint32_t d0[32];
           tmem_ld32(TM_Y + lane_off + (uint32_t)col0, d0);
           tmem_ld_wait();
-          ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], ds);
+          ds_pack_chunk_col(p0, d0, &s_delta[col0], ds);
         }
         {
           uint32_t d1[32];
           tmem_ld32(TM_Y + lane_off + (uint32_t)col0 + 32, d1);
           tmem_ld_wait();
-          ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], ds + 16);
+          ds_pack_chunk_col(p1, d1, &s_delta[col0 + 32], ds + 16);
         }
         tc_fence_before();   // Y has been read: after ds_ready the MMA warp may overwrite it with dQ^T
-        if ((has_next || vec_next) && tid < TILE) {
-          cp_async_wait_all();
-          if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
-        }
-        named_barrier_sync(2, 256);   // vector buffers: this step's reads done, next step's values visible
-        // dS^T goes into the dO stage of this step as a [key][query] tile (two [128][64] blocks,
-        // 128-byte swizzled): dV(s) was the last reader of the dO tile
-        mbar_wait(&dv_done, idx & 1u, ab);
+        // dS^T goes to X as a [key][query] tile (two [128][64] blocks, 128-byte swizzled) once the dQ
+        // tile of the previous step has left it
+        if (idx > 0) mbar_wait(&x_free, (idx - 1u) & 1u, ab);
         {
-          uint8_t* dst = sDO + (idx & 1u) * TILE_BYTES + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
+          uint8_t* dst = sX + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch)
             *reinterpret_cast<uint4*>(dst + (((uint32_t)ch ^ ((uint32_t)row & 7u)) << 4)) =
@@ -254,15 +263,25 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         }
         fence_proxy_async_smem();
         mbar_arrive_warp(&ds_ready);
+        // hand the vectors over: every warp has finished reading this step's, then the next step's land
+        named_barrier_sync(2, 256);
+        if ((has_next || vec_next) && tid < TILE) {
+          s_lse[tid] = l_nx;
+          s_delta[tid] = d_nx;
+          s_pos[tid] = p_nx;
+        }
+        named_barrier_sync(3, 256);
       }
 
-      // ---- epilogue: dK * scale, dV -> bf16 rows ----
+      // ---- epilogue: dK * scale, dV -> bf16 rows (staged through X, free once the last dQ tile has left) ----
       mbar_wait(&acc_done, n_items & 1u, ab);
+      mbar_wait(&x_free, (idx - 1u) & 1u, ab);
       tc_fence_after();
       ++n_items;
       {
         const long long row_off =
             key_valid ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0) : -1;
+        uint8_t* stage = sX + warp * 2048;
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
@@ -275,11 +294,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
-            store_patch_32x32(s_stage[warp], pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+            store_patch_32x32(stage, pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
           }
         }
       }
       tc_fence_before();
+      // X is the next item's dS^T tile: no warp may write it while another still stages its stores
+      named_barrier_sync(2, 256);
       ring_release(ring, n_ring);
       it = it_next;
       w = w_next;
@@ -289,13 +310,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   } else if (warp < FUSED_EW_WARPS + FUSED_DQ_WARPS) {
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
-    // and the 128 query rows of the step as columns. The tile goes to shared memory transposed, as
-    // fp32 [query row][128]: rows 0-63 into the Q tile of the step's stage, rows 64-127 into its
-    // dO / dS^T tile (32 KB each), from where two bulk reductions add it to dq_acc.
+    // and the 128 query rows of the step as columns. The whole row comes into registers in one round
+    // (Y is released right after it); then the tile goes through X transposed, as fp32
+    // [query row][128], 64 query rows at a time, and a bulk reduction adds each half to dq_acc.
     reg_dec_dq();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const bool issuer = (warp == FUSED_EW_WARPS) && (lane == 0);
+    float* stage = reinterpret_cast<float*>(sX) + quad * 32 + lane;
     uint32_t idx = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
@@ -308,11 +330,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       }
       for (int g = 0; g < G; ++g) {
         for (int i = it.i0; i < it.i_end; ++i, ++idx) {
-          const int hq = it.kvh * G + g;
+          const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
           const int nvalid = min(it.nsel - i * TILE, TILE);
-          const uint32_t st = idx & 1u;
-          float* stage_lo = reinterpret_cast<float*>(sQ + st * TILE_BYTES) + quad * 32 + lane;    // query rows 0-63
-          float* stage_hi = reinterpret_cast<float*>(sDO + st * TILE_BYTES) + quad * 32 + lane;   // query rows 64-127
           const bool ok = mbar_wait(&dq_full, idx & 1u, ab);
           tc_fence_after();
           uint32_t r0[32], r1[32], r2[32], r3[32];
@@ -323,30 +342,36 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
-          // dK of this step still reads the Q and dS^T tiles the staging overwrites
+          // dK of this step still reads dS^T from X
           mbar_wait(&dk_done, idx & 1u, ab);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) stage_lo[j * HEAD_DIM] = __uint_as_float(r0[j]);
+          for (int j = 0; j < 32; ++j) stage[j * HEAD_DIM] = __uint_as_float(r0[j]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) stage_lo[(32 + j) * HEAD_DIM] = __uint_as_float(r1[j]);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage_hi[j * HEAD_DIM] = __uint_as_float(r2[j]);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage_hi[(32 + j) * HEAD_DIM] = __uint_as_float(r3[j]);
+          for (int j = 0; j < 32; ++j) stage[(32 + j) * HEAD_DIM] = __uint_as_float(r1[j]);
           fence_proxy_async_smem();
           named_barrier_sync(4, FUSED_DQ_WARPS * 32);
-          if (issuer) {
-            // rows past the last valid query row of the tile hold exact zeros (their dS^T columns are
-            // zero); rows past the end of the accumulator are clipped by the tensor map
-            if (ok) {
-              const int x = hq * HEAD_DIM, y = it.bos_q + i * TILE;
-              tma_reduce_add_2d(&tm_dq, sQ + st * TILE_BYTES, x, y);
-              if (nvalid > 64) tma_reduce_add_2d(&tm_dq, sDO + st * TILE_BYTES, x, y + 64);
+          // rows past the last valid query row of the tile hold exact zeros (their dS^T columns are
+          // zero); rows past the end of the accumulator are clipped by the tensor map
+          if (issuer && ok) {
+            tma_reduce_add_2d(&tm_dq, sX, x, y);
+            bulk_commit_group();
+            bulk_wait_read_all();
+          }
+          named_barrier_sync(4, FUSED_DQ_WARPS * 32);   // the first half has been read out of X
+          if (nvalid > 64) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stage[j * HEAD_DIM] = __uint_as_float(r2[j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stage[(32 + j) * HEAD_DIM] = __uint_as_float(r3[j]);
+            fence_proxy_async_smem();
+            named_barrier_sync(4, FUSED_DQ_WARPS * 32);
+            if (issuer && ok) {
+              tma_reduce_add_2d(&tm_dq, sX, x, y + 64);
               bulk_commit_group();
               bulk_wait_read_all();
             }
-            mbar_arrive(&qdo_empty[st]);   // the stage may be refilled by the producer
           }
+          if (issuer) mbar_arrive(&x_free);   // X may take the next dS^T (or the item's output staging)
         }
       }
       ring_release(ring, n_ring);
@@ -394,11 +419,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           }
           const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
           const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
-          // the stage is free once the dQ tile staged in it (after dK and dQ^T of its step) has been reduced
-          mbar_wait(&qdo_empty[st], ph ^ 1u, ab);
+          mbar_wait(&q_empty[st], ph ^ 1u, ab);
           mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
           tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
           tma_load_2d(sQ + st * TILE_BYTES + BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
+          mbar_wait(&do_empty[st], ph ^ 1u, ab);
           mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
           tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
           tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
@@ -418,23 +443,24 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // S^T, dP^T: both operands K-major
     const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // dV, dK: B operand MN-major
     const uint32_t idesc_mm = umma_idesc_bf16(HEAD_DIM, TILE, 1, 1);   // dQ^T: both operands MN-major
-    const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+    const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO),
+                   x_base = smem_u32(sX);
     uint32_t q_iter = 0, n_items = 0;
 
     auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
       umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
                                    idesc_kk, 0u);
     };
-    auto issue_dv = [&](uint32_t a_tmem, uint32_t b_base, bool acc) {
-      umma_tile_k128<true, true, 2>(TM_DV, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
+    auto issue_dv = [&](uint32_t b_base, bool acc) {
+      umma_tile_k128<true, true, 2>(TM_DV, TM_X, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
     };
-    auto issue_dk = [&](uint32_t ds_base, uint32_t b_base, bool acc) {
-      umma_tile_k128<false, true>(TM_DK, umma_desc_sw128(ds_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
+    auto issue_dk = [&](uint32_t b_base, bool acc) {
+      umma_tile_k128<false, true>(TM_DK, umma_desc_sw128(x_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
                                   idesc_mn, acc ? 1u : 0u);
     };
-    auto issue_dq = [&](uint32_t ds_base) {
+    auto issue_dq = [&]() {
       umma_tile_k128<false, true, 0, 0, 8, true>(TM_Y, umma_desc_sw128(k_base, BLK_BYTES, 1024),
-                                                 umma_desc_sw128(ds_base, BLK_BYTES, 1024), idesc_mm, 0u);
+                                                 umma_desc_sw128(x_base, BLK_BYTES, 1024), idesc_mm, 0u);
     };
 
     for (uint32_t n_ring = 0;; ++n_ring) {
@@ -469,8 +495,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         const bool has_next = (s + 1 < n_steps);
         mbar_wait(&p_ready, q_iter & 1u, ab);
         tc_fence_after();
-        issue_dv(TM_X, do_base + st * TILE_BYTES, s > 0);
-        umma_commit(&dv_done);       // the dO tile of this stage may now be overwritten with dS^T
+        issue_dv(do_base + st * TILE_BYTES, s > 0);
+        umma_commit(&do_empty[st]);
         if (has_next) {
           mbar_wait(&q_full[st_n], ph_n, ab);
           tc_fence_after();
@@ -479,10 +505,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         }
         mbar_wait(&ds_ready, q_iter & 1u, ab);
         tc_fence_after();
-        issue_dq(do_base + st * TILE_BYTES);
+        issue_dq();
         umma_commit(&dq_full);
-        issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
-        umma_commit(&dk_done);       // the read-out warps may now stage dQ over the Q and dS^T tiles
+        issue_dk(q_base + st * TILE_BYTES, s > 0);
+        umma_commit(&dk_done);       // X may now take the dQ tile
+        umma_commit(&q_empty[st]);
         // every product that reads K / V has been issued: the next item's tiles may come in
         if (!has_next) umma_commit(&kv_free);
         if (has_next) {
@@ -536,7 +563,7 @@ int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, con
   LOGO_CHECK_CUDA(cudaGetDevice(&dev));
   if (attr_set_dev != dev) {
     LOGO_CHECK_CUDA(
-        cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
+        cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FusedSmem::BYTES));
     attr_set_dev = dev;
   }
   const int sms = sm_count();
@@ -547,7 +574,7 @@ int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, con
   const int rc = make_tmap_2d_f32(&tm_dq, dq_acc, (uint64_t)a.hq * HEAD_DIM, acc_rows, (uint64_t)a.hq * HEAD_DIM * 4,
                                   HEAD_DIM, 64);
   if (rc) return rc;
-  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, a);
+  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, FusedSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, a);
   prof_end(PROF_BWD_FUSED, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_FINISH, stream);

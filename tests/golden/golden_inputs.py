@@ -146,3 +146,40 @@ def rope_case():
     g = rs.standard_normal((n, h, d)).astype(np.float32)
     pos = rs.randint(0, 8192, size=n).astype(np.int64)
     return x, g, pos
+
+
+# ----------------------------------------------------------------------------------------------
+# model-level drop-in: a tiny LoGoForCausalLM (one LoGo layer, one dense layer)
+# ----------------------------------------------------------------------------------------------
+MODEL_CASE = dict(vocab_size=128, hidden_size=256, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                  num_key_value_heads=2, max_position_embeddings=1024, rms_norm_eps=1e-5, attn_type_list=[0, 1],
+                  window_size=128, global_qk_param="linear_proj", sparse_full_attn_backend="flash",
+                  gate_thres_init=0.5, tie_word_embeddings=False, seed=105)
+
+
+def model_weights(shapes, seed=MODEL_CASE["seed"]):
+    """Parameter / persistent-buffer name -> fp32 array for the tiny model, drawn in sorted name order.
+    ``shapes``: name -> shape, as ``{k: tuple(v.shape) for k, v in model.state_dict().items()}`` gives it."""
+    rs = np.random.RandomState(seed)
+    w = {}
+    for name in sorted(shapes):
+        shape = tuple(shapes[name])
+        if name.endswith("gate_thres"):
+            w[name] = np.full(shape, 0.5, dtype=np.float32)
+        elif name.endswith("_global_proj"):
+            w[name] = (np.eye(shape[-1], dtype=np.float32)[None] + 0.02 * rs.standard_normal(shape)).astype(np.float32)
+        elif "norm" in name:
+            w[name] = (1 + 0.1 * rs.standard_normal(shape)).astype(np.float32)
+        elif "embed_tokens" in name:
+            w[name] = (0.5 * rs.standard_normal(shape)).astype(np.float32)
+        else:
+            w[name] = (0.05 * rs.standard_normal(shape)).astype(np.float32)
+    return w
+
+
+def model_inputs():
+    """(packed ids [1, 200], cu_seqlens, batch ids [2, 154]) for the packed forward and the prefill + decode loop."""
+    rs = np.random.RandomState(MODEL_CASE["seed"] + 1)
+    packed = rs.randint(0, MODEL_CASE["vocab_size"], size=(1, 200)).astype(np.int64)
+    batch = rs.randint(0, MODEL_CASE["vocab_size"], size=(2, 154)).astype(np.int64)
+    return packed, [0, 90, 90, 200], batch

@@ -37,7 +37,8 @@ sys.path.insert(0, REF)
 sys.path.insert(0, str(OUT))
 
 from golden_inputs import (attn_case_inputs, layer_case_inputs, selection_cases, layer_weights,  # noqa: E402
-                           dense_attn_inputs, dense_attn_weights, ATTN_CASES, DENSE_ATTN_CASE, LAYER_CASES)
+                           dense_attn_inputs, dense_attn_weights, model_inputs, model_weights, ATTN_CASES,
+                           DENSE_ATTN_CASE, LAYER_CASES, MODEL_CASE)
 
 
 @triton.jit
@@ -304,11 +305,42 @@ def gen_rope():
     print("rope.npz")
 
 
+def gen_model():
+    """A tiny LoGoForCausalLM (one LoGo layer + one dense layer) through the reference's own model code:
+    logits of a packed varlen batch, and of a prefill followed by four single-token steps through its Cache."""
+    from logo.cache import Cache
+    from logo.configuration_logo import LoGoConfig
+    from logo.modeling_logo import LoGoForCausalLM
+    cfg = LoGoConfig(**{k: v for k, v in MODEL_CASE.items() if k != "seed"})
+    model = LoGoForCausalLM(cfg).eval()
+    shapes = {k: tuple(v.shape) for k, v in model.state_dict().items()}
+    model.load_state_dict({k: torch.from_numpy(v) for k, v in model_weights(shapes).items()})
+    packed, cu, batch = model_inputs()
+    out = {}
+    with torch.no_grad():
+        y = model(input_ids=torch.from_numpy(packed), cu_seqlens=torch.tensor(cu, dtype=torch.int32), use_cache=False)
+        out["model/packed_logits"] = y.logits[0].numpy()
+        B, T0, steps = batch.shape[0], 150, 4
+        ids = torch.from_numpy(batch)
+        cache = Cache()
+        y = model(input_ids=ids[:, :T0], past_key_values=cache, use_cache=True)
+        logits = [y.logits]
+        for s in range(steps):
+            y = model(input_ids=ids[:, T0 + s: T0 + s + 1], past_key_values=cache, use_cache=True)
+            logits.append(y.logits)
+        out["model/cached_logits"] = torch.cat(logits, dim=1).numpy()
+        full = model(input_ids=ids, use_cache=False).logits.numpy()
+    out["model/param_names"] = np.array(sorted(shapes))
+    print("model: logits std", float(out["model/packed_logits"].std()), "max |cached - full|",
+          float(np.abs(out["model/cached_logits"] - full).max()))
+    np.savez_compressed(OUT / "model.npz", **out)
+
+
 if __name__ == "__main__":
     import sys
     torch.set_num_threads(8)
     install_shims()
     gens = {"selection": gen_selection, "attention": gen_attention, "layer": gen_layer, "decode": gen_decode,
-            "misc": gen_misc, "rope": gen_rope}
+            "misc": gen_misc, "rope": gen_rope, "model": gen_model}
     for name in (sys.argv[1:] or list(gens)):       # `make_golden.py rope` regenerates one fixture only
         gens[name]()
