@@ -861,6 +861,95 @@ def run_decode_model(args):
                      "peak_source": f"{peaks['source']} copy bandwidth"}}))
 
 
+def run_ref_gpu(args):
+    """The reference's OWN GPU kernels on this GPU (the kernels to beat): its Triton ``sq_full_attn``
+    (logo/ops/selected_full_attn.py, unmodified, JIT-compiled here) forward + backward on the headline
+    configuration for the four ratios, and the flash-attn call of its local branch (window 128).
+    Needs the reference package under baseline/_ref (pip install --target); a part that does not run
+    on this box is reported as unavailable with the error text."""
+    ref = ROOT / "baseline" / "_ref"
+    out = {"metric": "reference_gpu_kernels", "n_gpus": 1, "data": "synthetic", "dtype": "bf16",
+           "config": {"workload": "reference Triton sq_full_attn fwd+bwd, 4x8192 tokens packed [1,32768,16,128]; "
+                                  "flash-attn varlen window-128 fwd+bwd on the same tokens"}}
+    if not (ref / "logo").is_dir():
+        out["unavailable"] = "no reference package under baseline/_ref"
+        print(json.dumps(out))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --workload ref_gpu needs a CUDA device")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    sys.path.insert(0, str(ref))
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    try:
+        from logo.ops import sq_full_attn as ref_sq_full_attn
+
+        # a small case first: does the JIT produce kernels for this GPU at all?
+        n0 = 1024
+        q0, k0, v0 = (torch.randn(1, n0, 2, D, device=device, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+        o0 = ref_sq_full_attn(q0, k0, v0, torch.rand(1, n0, device=device) < 0.5,
+                              cu_seqlens=torch.tensor([0, n0], dtype=torch.int32, device=device))
+        o0.sum().backward()
+        torch.cuda.synchronize()
+        res = {}
+        for r in (0.125, 0.25, 0.5, 1.0):
+            q, k, v, do, sel, cu = make_batch(device, r, seed=1234)
+            q, k, v = (t[None].requires_grad_(True) for t in (q, k, v))
+            f_step = 3.5 * effective_flops_fwd(sel)
+
+            def step():
+                q.grad = k.grad = v.grad = None
+                o = ref_sq_full_attn(q, k, v, sel[None], scale=SCALE, cu_seqlens=cu)
+                o.backward(do[None])
+
+            ms = timed(step, args.steps, max(args.warmup, 2))
+            res[f"{r:g}"] = {"ms_per_step": ms, "tflops": f_step / (ms * 1e-3) / 1e12}
+            del q, k, v, do
+        out["triton_sq_full_attn"] = res
+    except Exception as exc:   # noqa: BLE001
+        out["triton_sq_full_attn"] = {"unavailable": f"unavailable on this box: {type(exc).__name__}: {exc}"[:400]}
+        torch.cuda.synchronize()
+    try:
+        from flash_attn import flash_attn_varlen_func
+
+        q, k, v, do, _, cu = make_batch(device, 1.0, seed=1234)
+        q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+
+        def step_l():
+            q.grad = k.grad = v.grad = None
+            o = flash_attn_varlen_func(q, k, v, cu, cu, T_SEQ, T_SEQ, softmax_scale=SCALE, causal=True,
+                                       window_size=(128, 128))
+            o.backward(do)
+
+        ms = timed(step_l, args.steps, max(args.warmup, 2))
+        out["flash_attn_window128"] = {"ms_per_step": ms}
+        # this package's local branch on the same tensors, for the ratio
+        from logo_b200 import ops
+        ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+
+        def step_m():
+            ql.grad = kl.grad = vl.grad = None
+            o = ops.swa_attn(ql, kl, vl, cu, 128, SCALE)
+            o.backward(do)
+
+        out["logo_b200_window128"] = {"ms_per_step": timed(step_m, args.steps, max(args.warmup, 2))}
+    except Exception as exc:   # noqa: BLE001
+        out["flash_attn_window128"] = {"unavailable": f"unavailable on this box: {type(exc).__name__}: {exc}"[:400]}
+    print(json.dumps(out))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -889,7 +978,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ratio", type=float, default=0.5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "decode_model", "fuse", "layer", "prefill"],
+    ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "decode_model", "fuse", "layer", "prefill", "ref_gpu"],
                     help="sq_attn is the headline metric; the others measure further rows of the same path")
     ap.add_argument("--decode-batch", type=int, default=0, help="sequences of the decode workloads (0: by rank count)")
     ap.add_argument("--no-legs", action="store_true", help="headline only: leave out the fuse / decode / layer / prefill legs")
@@ -904,6 +993,8 @@ def main():
         run_gpu(args)
     elif args.workload == "decode_model":
         run_decode_model(args)
+    elif args.workload == "ref_gpu":
+        run_ref_gpu(args)
     else:
         run_one_leg(args)
 

@@ -8,13 +8,13 @@
 //     dP^T = V dO^T           -> TMEM Y
 //     P^T  = exp2(S^T c - lse) masked, bf16       -> written into X (the A operand of dV)
 //     dV  += P^T dO                               (A from TMEM, B = dO tile read MN-major)
-//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory (tile X) as a
-//                                                    [key][query] tile
+//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory as a [key][query]
+//                                                    tile, into the dO stage dV has finished with
 //     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
 //     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
 // dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
-// dedicated warps, laid down as an fp32 [query][head dim] tile in X (once dK has consumed dS^T),
-// 64 query rows at a time, and added to an fp32 accumulator in global memory by bulk tensor
+// dedicated warps, laid down as an fp32 [query][head dim] tile in a 32 KB staging tile X, 64 query
+// rows at a time, and added to an fp32 accumulator in global memory by bulk tensor
 // reductions (cp.reduce.async.bulk: the reduction runs in L2 on whole lines; per-thread
 // red.global.add was measured 2.5x slower, bound by the SM's atomic issue rate).
 // bwd_dq_finish_kernel scales, converts and scatters the accumulator to the token rows afterwards.
@@ -64,9 +64,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   uint8_t* sK = smem + FusedSmem::K;
   uint8_t* sV = smem + FusedSmem::V;
   uint8_t* sQ = smem + FusedSmem::Q;      // 2 stages
-  uint8_t* sDO = smem + FusedSmem::DO;    // 2 stages
-  // X: dS^T of the step ([key][query] bf16), then the two halves of its dQ tile ([query][128] fp32) on
-  // their way to the bulk reduction; at the end of an item the staging of the dK / dV stores
+  uint8_t* sDO = smem + FusedSmem::DO;    // 2 stages; stage s & 1 holds dS^T of step s once dV(s) is done
+  // X: the two halves of a step's dQ tile ([query][128] fp32) on their way to the bulk reduction; at
+  // the end of an item the staging of the dK / dV stores
   uint8_t* sX = smem + FusedSmem::X;
   float* s_lse = reinterpret_cast<float*>(smem + FusedSmem::LSE);
   float* s_delta = reinterpret_cast<float*>(smem + FusedSmem::DELTA);
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FusedSmem::BARS);
   uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
            *do_empty = bars + 8, &st_full = bars[10], &dpt_full = bars[11], &p_ready = bars[12], &ds_ready = bars[13],
-           &dq_full = bars[14], &dk_done = bars[15], &dq_read = bars[16], &x_free = bars[17], &acc_done = bars[18];
+           &dq_full = bars[14], &dv_done = bars[15], &dq_read = bars[16], &x_free = bars[17], &acc_done = bars[18];
   const ItemRing ring{reinterpret_cast<int*>(smem + FusedSmem::ITEMS), bars + 19, bars + 19 + ITEM_RING};
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + FusedSmem::MISC);
   int& abort_flag = *reinterpret_cast<int*>(smem + FusedSmem::MISC + 4);
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     mbar_init(&p_ready, FUSED_EW_WARPS);    // one arrival per warp
     mbar_init(&ds_ready, FUSED_EW_WARPS);
     mbar_init(&dq_full, 1);
-    mbar_init(&dk_done, 1);
+    mbar_init(&dv_done, 1);
     mbar_init(&dq_read, FUSED_DQ_WARPS);
     mbar_init(&x_free, 1);
     mbar_init(&acc_done, 1);
@@ -251,11 +251,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           ds_pack_chunk_col(p1, d1, &s_delta[col0 + 32], ds + 16);
         }
         tc_fence_before();   // Y has been read: after ds_ready the MMA warp may overwrite it with dQ^T
-        // dS^T goes to X as a [key][query] tile (two [128][64] blocks, 128-byte swizzled) once the dQ
-        // tile of the previous step has left it
-        if (idx > 0) mbar_wait(&x_free, (idx - 1u) & 1u, ab);
+        // dS^T goes into the dO stage of this step as a [key][query] tile (two [128][64] blocks,
+        // 128-byte swizzled): dV(s) was the last reader of the dO tile
+        mbar_wait(&dv_done, idx & 1u, ab);
         {
-          uint8_t* dst = sX + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
+          uint8_t* dst = sDO + (idx & 1u) * TILE_BYTES + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch)
             *reinterpret_cast<uint4*>(dst + (((uint32_t)ch ^ ((uint32_t)row & 7u)) << 4)) =
@@ -299,8 +299,6 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         }
       }
       tc_fence_before();
-      // X is the next item's dS^T tile: no warp may write it while another still stages its stores
-      named_barrier_sync(2, 256);
       ring_release(ring, n_ring);
       it = it_next;
       w = w_next;
@@ -342,8 +340,6 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
-          // dK of this step still reads dS^T from X
-          mbar_wait(&dk_done, idx & 1u, ab);
 #pragma unroll
           for (int j = 0; j < 32; ++j) stage[j * HEAD_DIM] = __uint_as_float(r0[j]);
 #pragma unroll
@@ -370,8 +366,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
               bulk_commit_group();
               bulk_wait_read_all();
             }
+            named_barrier_sync(4, FUSED_DQ_WARPS * 32);   // the second half has been read out of X
           }
-          if (issuer) mbar_arrive(&x_free);   // X may take the next dS^T (or the item's output staging)
+          if (issuer) mbar_arrive(&x_free);   // X may take the item's output staging
         }
       }
       ring_release(ring, n_ring);
@@ -443,8 +440,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // S^T, dP^T: both operands K-major
     const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // dV, dK: B operand MN-major
     const uint32_t idesc_mm = umma_idesc_bf16(HEAD_DIM, TILE, 1, 1);   // dQ^T: both operands MN-major
-    const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO),
-                   x_base = smem_u32(sX);
+    const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
     uint32_t q_iter = 0, n_items = 0;
 
     auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
@@ -454,13 +450,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     auto issue_dv = [&](uint32_t b_base, bool acc) {
       umma_tile_k128<true, true, 2>(TM_DV, TM_X, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
     };
-    auto issue_dk = [&](uint32_t b_base, bool acc) {
-      umma_tile_k128<false, true>(TM_DK, umma_desc_sw128(x_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
+    auto issue_dk = [&](uint32_t ds_base, uint32_t b_base, bool acc) {
+      umma_tile_k128<false, true>(TM_DK, umma_desc_sw128(ds_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
                                   idesc_mn, acc ? 1u : 0u);
     };
-    auto issue_dq = [&]() {
+    auto issue_dq = [&](uint32_t ds_base) {
       umma_tile_k128<false, true, 0, 0, 8, true>(TM_Y, umma_desc_sw128(k_base, BLK_BYTES, 1024),
-                                                 umma_desc_sw128(x_base, BLK_BYTES, 1024), idesc_mm, 0u);
+                                                 umma_desc_sw128(ds_base, BLK_BYTES, 1024), idesc_mm, 0u);
     };
 
     for (uint32_t n_ring = 0;; ++n_ring) {
@@ -496,7 +492,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         mbar_wait(&p_ready, q_iter & 1u, ab);
         tc_fence_after();
         issue_dv(do_base + st * TILE_BYTES, s > 0);
-        umma_commit(&do_empty[st]);
+        umma_commit(&dv_done);       // the dO tile of this stage may now be overwritten with dS^T
         if (has_next) {
           mbar_wait(&q_full[st_n], ph_n, ab);
           tc_fence_after();
@@ -505,11 +501,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         }
         mbar_wait(&ds_ready, q_iter & 1u, ab);
         tc_fence_after();
-        issue_dq();
+        issue_dq(do_base + st * TILE_BYTES);
         umma_commit(&dq_full);
-        issue_dk(q_base + st * TILE_BYTES, s > 0);
-        umma_commit(&dk_done);       // X may now take the dQ tile
-        umma_commit(&q_empty[st]);
+        issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
+        umma_commit(&q_empty[st]);   // Q and dS^T of this stage have been consumed: both tiles may be refilled
+        umma_commit(&do_empty[st]);
         // every product that reads K / V has been issued: the next item's tiles may come in
         if (!has_next) umma_commit(&kv_free);
         if (has_next) {

@@ -71,7 +71,12 @@ class RotaryEmbedding(nn.Module):
 
     def __init__(self, config, device=None):
         super().__init__()
-        if getattr(config, "rope_scaling", None) is not None:
+        scaling = getattr(config, "rope_scaling", None)
+        if isinstance(scaling, dict):     # transformers >= 5 fills in {"rope_type": "default", ...} by itself
+            kind = scaling.get("rope_type", scaling.get("type", "default"))
+        else:
+            kind = "default" if scaling is None else str(scaling)
+        if kind != "default":
             raise NotImplementedError("only the default rope type is built in; pass position_embeddings for others")
         self.rope_type = "default"
         self.max_seq_len_cached = config.max_position_embeddings
