@@ -300,6 +300,28 @@ int logo_decode_attn(const void* q_local, const void* q_global, const void* k_ri
                      int32_t* status, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Language-model loss over lm_head logits. Replaces the label shift, the packed-boundary masking and
+ * the CrossEntropyLoss of logo/modeling_logo.py:380-407.
+ *
+ * logo_shift_labels: targets[i] = labels[i + 1] for every token that has a successor INSIDE its packed
+ *   sequence, ignore_index otherwise (the reference shifts logits / labels by one and sets
+ *   shift_labels[cu_seqlens[1:-1] - 1] = -100, :392-394); n_valid [1] int32 receives the number of
+ *   targets that are not ignore_index (the denominator of the mean).
+ * logo_ce_rows: for each of `rows` rows of bf16 logits (row r at logits + r * row_stride elements;
+ *   vocab and row_stride multiples of 8): row_loss[r] = logsumexp(row) - row[target] in fp32 (0 for an
+ *   ignored row). With write_grad != 0 the row is then overwritten in place by the gradient of
+ *   upstream * mean loss, (softmax(row) - onehot(target)) * upstream / *n_valid, as bf16 (zeros for an
+ *   ignored row): the caller multiplies it with the lm_head weight / the hidden states and never holds
+ *   fp32 logits (the reference upcasts the whole [tokens, vocab] tensor, :385).
+ * ------------------------------------------------------------------------------------------ */
+int logo_shift_labels(const int64_t* labels, const int32_t* cu_seqlens, int n_seq, int n_tokens,
+                      long long ignore_index, int64_t* targets, int32_t* n_valid, logo_stream_t stream);
+
+int logo_ce_rows(void* logits, long long row_stride, const int64_t* targets, long long ignore_index, float* row_loss,
+                 const int32_t* n_valid, float upstream, int rows, int vocab, int write_grad, int32_t* status,
+                 logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Per-kernel timing for benchmarks (no counterpart in the reference). While enabled on the
  * calling host thread, every launch of the kernels below is bracketed by CUDA events on its
  * stream. logo_profile_read waits for those events, returns per kernel kind the summed device

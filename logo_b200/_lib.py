@@ -60,6 +60,9 @@ _SIGNATURES = {
     "logo_decode_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "logo_shift_labels": (c_int, [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p]),
+    "logo_ce_rows": (c_int, [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                             c_void_p, c_void_p]),
     "logo_profile_enable": (c_int, [c_int]),
     "logo_profile_reserve": (c_int, [c_int]),
     "logo_profile_read": (c_int, [c_void_p, c_void_p, c_int]),

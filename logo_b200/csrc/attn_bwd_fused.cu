@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
 
       // ---- epilogue: dK * scale, dV -> bf16 rows (staged through X, free once the last dQ tile has left) ----
       mbar_wait(&acc_done, n_items & 1u, ab);
-      mbar_wait(&x_free, (idx - 1u) & 1u, ab);
+      mbar_wait(&x_free, n_items & 1u, ab);
       tc_fence_after();
       ++n_items;
       {
@@ -368,9 +368,11 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
             }
             named_barrier_sync(4, FUSED_DQ_WARPS * 32);   // the second half has been read out of X
           }
-          if (issuer) mbar_arrive(&x_free);   // X may take the item's output staging
         }
       }
+      // one phase per ITEM (a waiter must see every phase of a barrier, and the element-wise warps only
+      // look at this one at the end of an item): X may take the item's output staging
+      if (issuer) mbar_arrive(&x_free);
       ring_release(ring, n_ring);
     }
     if (issuer) bulk_wait_all();

@@ -29,6 +29,7 @@ __all__ = [
     "get_err_ratio",
     "assert_close",
     "check_device_status",
+    "lm_head_cross_entropy",
 ]
 
 HEAD_DIM = 128
@@ -489,3 +490,80 @@ class FuseFunction(torch.autograd.Function):
 def fuse_norm_blend(local, glob, gate, thres, w_local, w_global, eps: float, use_norm: bool = True):
     """local, glob [N,H,128] bf16; gate [N] or [N,1] bf16; thres one-element tensor. Returns [N, H*128]."""
     return FuseFunction.apply(local, glob, gate, thres, w_local, w_global, eps, use_norm)
+
+
+# ----------------------------------------------------------------------------------------
+# lm_head + shifted cross-entropy with packed-boundary masking (logo/modeling_logo.py:380-407)
+# ----------------------------------------------------------------------------------------
+class LmHeadLossFunction(torch.autograd.Function):
+    """Mean next-token cross-entropy of ``hidden @ weight.T`` without ever holding the ``[tokens, vocab]``
+    logits: rows are processed in chunks; each chunk's bf16 logits are turned into their gradient in
+    place by the loss kernel and immediately contracted into the gradients of ``hidden`` and ``weight``."""
+
+    @staticmethod
+    @_fwd_plain
+    def forward(ctx, hidden, weight, labels, cu_seqlens, ignore_index, chunk_rows):
+        lib = _lib.load()
+        _require_cuda(hidden, weight, labels)
+        if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+            raise TypeError("lm_head_cross_entropy takes bf16 hidden states and a bf16 weight")
+        n, hid = hidden.shape
+        vocab = weight.shape[0]
+        dev = hidden.device
+        hidden, weight = hidden.contiguous(), weight.contiguous()
+        labels = labels.reshape(-1).to(torch.int64).contiguous()
+        cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+        targets = torch.empty(n, dtype=torch.int64, device=dev)
+        n_valid = torch.zeros(1, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        row_loss = torch.empty(n, dtype=torch.float32, device=dev)
+        stream = _lib.current_stream_ptr(dev)
+        need_h, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        d_hidden = torch.empty_like(hidden) if need_h else None
+        d_weight = torch.zeros(vocab, hid, dtype=torch.float32, device=dev) if need_w else None
+        with _lib.on_device(hidden):
+            _lib.check(lib.logo_shift_labels(labels.data_ptr(), cu.data_ptr(), cu.numel() - 1, n, int(ignore_index),
+                                             targets.data_ptr(), n_valid.data_ptr(), stream), "logo_shift_labels")
+            for a in range(0, n, chunk_rows):
+                b = min(a + chunk_rows, n)
+                logits = hidden[a:b] @ weight.t()                       # bf16, as the bf16 lm_head produces them
+                _lib.check(lib.logo_ce_rows(logits.data_ptr(), vocab, targets[a:b].data_ptr(), int(ignore_index),
+                                            row_loss[a:b].data_ptr(), n_valid.data_ptr(), 1.0, b - a, vocab,
+                                            int(need_h or need_w), status.data_ptr(), stream), "logo_ce_rows")
+                if need_h:
+                    torch.mm(logits, weight, out=d_hidden[a:b])
+                if need_w:
+                    d_weight += (logits.t() @ hidden[a:b]).float()
+        ctx.save_for_backward(d_hidden, d_weight.to(weight.dtype) if need_w else None)
+        ctx.status = status
+        return row_loss.sum() / n_valid.clamp(min=1).to(torch.float32)
+
+    @staticmethod
+    @_bwd
+    def backward(ctx, g):
+        d_hidden, d_weight = ctx.saved_tensors
+        return (None if d_hidden is None else d_hidden * g.to(d_hidden.dtype),
+                None if d_weight is None else d_weight * g.to(d_weight.dtype), None, None, None, None)
+
+
+def lm_head_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                          cu_seqlens: Optional[torch.Tensor] = None, ignore_index: int = -100,
+                          chunk_rows: int = 8192) -> torch.Tensor:
+    """The loss of ``LoGoForCausalLM.forward`` (logo/modeling_logo.py:380-407) from the final hidden states.
+
+    ``hidden`` ``[B, T, H]`` or packed ``[1, N, H]`` / ``[N, H]`` bf16, ``weight`` the lm_head weight ``[V, H]``
+    bf16 (V a multiple of 8), ``labels`` the UN-shifted labels with the shape of the tokens. Token ``i`` is
+    scored against ``labels[i + 1]``; the last token of every row -- or, with ``cu_seqlens``, of every
+    packed sequence -- has no target, as have labels equal to ``ignore_index``. Returns the mean over the
+    scored tokens as an fp32 scalar; differentiable with respect to ``hidden`` and ``weight``.
+    """
+    if hidden.dim() == 3:
+        bsz, t, hid = hidden.shape
+        flat = hidden.reshape(bsz * t, hid)
+        if cu_seqlens is None:
+            cu_seqlens = torch.arange(0, (bsz + 1) * t, t, dtype=torch.int32, device=hidden.device)
+    else:
+        flat = hidden
+        if cu_seqlens is None:
+            cu_seqlens = torch.tensor([0, hidden.shape[0]], dtype=torch.int32, device=hidden.device)
+    return LmHeadLossFunction.apply(flat, weight, labels, cu_seqlens, ignore_index, chunk_rows)

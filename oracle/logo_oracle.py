@@ -361,6 +361,22 @@ class CacheRef:
 
 
 # ---------------------------------------------------------------------------------------
+# language-model loss
+# ---------------------------------------------------------------------------------------
+def lm_loss_ref(logits: torch.Tensor, labels: torch.Tensor, cu_seqlens: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """logo/modeling_logo.py:380-407: logits [B, T, V] (or [1, N, V] packed), labels like the tokens.
+    Upcast, shift by one, do not predict across packed-sequence boundaries, mean cross-entropy."""
+    vocab = logits.shape[-1]
+    logits = logits.float()                                            # :385
+    shift_logits = logits[..., :-1, :].contiguous().view(-1, vocab)    # :386-389
+    shift_labels = labels[..., 1:].contiguous().view(-1).clone()       # :387-390
+    if cu_seqlens is not None:
+        cu = torch.as_tensor([int(x) for x in cu_seqlens], dtype=torch.int64)
+        shift_labels[cu[1:-1] - 1] = -100                              # :392-394
+    return torch.nn.functional.cross_entropy(shift_logits, shift_labels, ignore_index=-100)   # :406
+
+
+# ---------------------------------------------------------------------------------------
 # budget controller
 # ---------------------------------------------------------------------------------------
 def update_gate_thres_ref(gate_thres: np.ndarray, global_count: np.ndarray, total_count: np.ndarray,

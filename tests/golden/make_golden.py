@@ -320,6 +320,13 @@ def gen_model():
     with torch.no_grad():
         y = model(input_ids=torch.from_numpy(packed), cu_seqlens=torch.tensor(cu, dtype=torch.int32), use_cache=False)
         out["model/packed_logits"] = y.logits[0].numpy()
+        # the reference's loss (shifted labels, packed boundaries masked, logo/modeling_logo.py:380-407)
+        y = model(input_ids=torch.from_numpy(packed), labels=torch.from_numpy(packed),
+                  cu_seqlens=torch.tensor(cu, dtype=torch.int32), use_cache=False)
+        out["model/packed_loss"] = np.array([float(y.loss)])
+        y = model(input_ids=torch.from_numpy(batch), labels=torch.from_numpy(batch), use_cache=False)
+        out["model/batch_loss"] = np.array([float(y.loss)])
+        out["model/batch_logits"] = y.logits.numpy()
         B, T0, steps = batch.shape[0], 150, 4
         ids = torch.from_numpy(batch)
         cache = Cache()
