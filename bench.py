@@ -981,10 +981,15 @@ def main():
     ap.add_argument("--workload", default="sq_attn", choices=["sq_attn", "decode", "decode_model", "fuse", "layer", "prefill", "ref_gpu"],
                     help="sq_attn is the headline metric; the others measure further rows of the same path")
     ap.add_argument("--decode-batch", type=int, default=0, help="sequences of the decode workloads (0: by rank count)")
+    ap.add_argument("--bwd-mode", default=None, choices=["single_pass", "two_kernel"],
+                    help="backward implementation of the global branch (default: the library's)")
     ap.add_argument("--no-legs", action="store_true", help="headline only: leave out the fuse / decode / layer / prefill legs")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: leave out the CPU baseline leg")
     args = ap.parse_args()
+    if args.bwd_mode and args.impl == "ours":
+        import logo_b200
+        logo_b200.set_backward_mode("global", args.bwd_mode)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

@@ -184,3 +184,16 @@ def test_rope_bf16_graph_bit_exact(golden):
     out.backward(torch.from_numpy(grad_out).to(torch.bfloat16))
     np.testing.assert_array_equal(out.detach().float().numpy(), g["out"])
     np.testing.assert_array_equal(xt.grad.float().numpy(), g["grad"])
+
+
+def test_lm_loss_matches_reference_model_loss(golden):
+    """The oracle's restatement of the loss (label shift, packed-boundary masking, mean cross-entropy) on
+    the reference model's own logits reproduces the loss the reference model returned."""
+    from golden_inputs import model_inputs
+
+    g = golden["model"]
+    packed, cu, batch = model_inputs()
+    loss = orc.lm_loss_ref(torch.from_numpy(g["model/packed_logits"])[None], torch.from_numpy(packed), cu)
+    assert abs(float(loss) - float(g["model/packed_loss"][0])) < 1e-5
+    loss = orc.lm_loss_ref(torch.from_numpy(g["model/batch_logits"]), torch.from_numpy(batch), None)
+    assert abs(float(loss) - float(g["model/batch_loss"][0])) < 1e-5
