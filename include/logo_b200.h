@@ -266,6 +266,25 @@ int logo_rope(const void* x, long long x_stride_tok, long long x_stride_head, vo
               const void* sin, int n_tokens, int heads, int d, int inverse, logo_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Per-head re-parameterisation of the global branch fused with the rotary embedding. Replaces the
+ * einsum of logo/layers/logo.py:86-94 ('b l h d, h d e -> b l h e'), apply_rotary_pos_emb at
+ * logo/layers/logo.py:137-139 and the transpose / contiguous copies of :156-158 for one tensor:
+ *     out[t, h, :] = rope( bf16( x[t, h, :] @ w[h] ) )
+ *   x    bf16 rows of heads * 128 at x_stride elements (a multiple of 8) per token
+ *   w    bf16 [heads, 128, 128] ([head][in][out], the layout of q/k/v_global_proj)
+ *   rows NULL: every token. Otherwise the ascending token indices to compute (q_idx of
+ *        logo_select_rows) with their count in the device scalar n_rows: only those rows of `out`
+ *        are written -- the global QUERY projection is needed for selected rows only.
+ *   cos_t, sin_t [n_tokens, 128] bf16, or both NULL for no rotation (the value projection)
+ *   out  bf16 [n_tokens, heads * 128], token-major
+ * The product is rounded to bf16 before the rotation, and the rotation keeps the three bf16 roundings
+ * of the eager expression (as logo_rope does).
+ * ------------------------------------------------------------------------------------------ */
+int logo_proj_rope(const void* x, long long x_stride, const void* w, const int64_t* rows, const int32_t* n_rows,
+                   const void* cos_t, const void* sin_t, void* out, int n_tokens, int heads, int d, int32_t* status,
+                   logo_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * KV cache (bf16, head-major):
  *   global branch: k_cache, v_cache [batch, h, t_max, 128]; token p of a sequence sits at row p
  *   local branch : k_ring,  v_ring  [batch, h, ring, 128];  token p sits at row p % ring

@@ -53,6 +53,8 @@ _SIGNATURES = {
     "logo_silu_mul": (c_int, [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p]),
     "logo_rope": (c_int, [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_void_p]),
+    "logo_proj_rope": (c_int, [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_int, c_void_p, c_void_p]),
     "logo_cache_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p, c_void_p]),

@@ -237,38 +237,59 @@ class LoGoAttention(nn.Module):
         query_states = self.q_proj(hidden_states)
         key_states = self.k_proj(hidden_states)
         value_states = self.v_proj(hidden_states)
-        gq, gk, gv = self._transform_qkv(query_states, key_states, value_states)
         gate = torch.sigmoid(self.gate_proj(hidden_states))              # [B, T, 1]
         if query_states.dtype != torch.bfloat16:
             raise TypeError("logo_b200.LoGoAttention needs bf16 activations (cast the model or use autocast)")
+        n_tok = bsz * q_len
+        is_decode = past_key_value is not None and q_len == 1
+        filled = 0
+        if past_key_value is not None:
+            if not isinstance(past_key_value, Cache):
+                raise TypeError("the cache must be a logo_b200.Cache")
+            filled = (past_key_value.layers[self.layer_idx].length
+                      if len(past_key_value.layers) > self.layer_idx else 0)
+        # Prefill / training with the per-head projection: one kernel per global tensor does projection,
+        # rotary embedding and layout, and the query projection runs over the selected rows only. Decode
+        # steps, continuations of a filled cache and the scale / offset parameterisation take the eager route.
+        fused_proj = self.global_qk_param == "linear_proj" and not is_decode and filled == 0
 
         # token-major [B, T, H, D]: the layout the kernels consume, no transposes
         q_l = query_states.view(bsz, q_len, H, D)
         k_l = key_states.view(bsz, q_len, HKV, D)
         v_l = value_states.view(bsz, q_len, HKV, D)
-        q_g, k_g, v_g = gq.reshape(bsz, q_len, H, D), gk.reshape(bsz, q_len, HKV, D), gv.view(bsz, q_len, HKV, D)
 
         if position_embeddings is None:
             cos, sin = self.rotary_emb(v_l, position_ids)
         else:
             cos, sin = position_embeddings
         # rotary embedding of both branches (logo/layers/logo.py:136-139): one kernel per tensor
-        n_tok = bsz * q_len
         # tables may come with a broadcast batch of 1 (the reference multiplies with broadcasting)
         cos2 = cos.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
         sin2 = sin.expand(bsz, q_len, D).reshape(n_tok, D).to(torch.bfloat16)
+        gate_flat = gate.reshape(-1).to(torch.bfloat16)
+        sel = None
+        if fused_proj:
+            if cu_seqlens is not None:
+                cu = cu_seqlens
+            else:  # equal-length batch packed to one varlen batch (logo.py:200-209)
+                cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
+            sel = ops.select_rows(gate_flat, self.gate_thres, cu)
+            q_g = ops.proj_rope(query_states.view(n_tok, H, D), self.q_global_proj, cos2, sin2, sel).view(bsz, q_len, H, D)
+            k_g = ops.proj_rope(key_states.view(n_tok, HKV, D), self.k_global_proj, cos2, sin2).view(bsz, q_len, HKV, D)
+            v_g = ops.proj_rope(value_states.view(n_tok, HKV, D), self.v_global_proj).view(bsz, q_len, HKV, D)
+        else:
+            gq, gk, gv = self._transform_qkv(query_states, key_states, value_states)
+            q_g, k_g, v_g = gq.reshape(bsz, q_len, H, D), gk.reshape(bsz, q_len, HKV, D), gv.view(bsz, q_len, HKV, D)
+            q_g = ops.rope(q_g.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
+            k_g = ops.rope(k_g.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
         q_l = ops.rope(q_l.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
         k_l = ops.rope(k_l.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
-        q_g = ops.rope(q_g.reshape(n_tok, H, D), cos2, sin2).view(bsz, q_len, H, D)
-        k_g = ops.rope(k_g.reshape(n_tok, HKV, D), cos2, sin2).view(bsz, q_len, HKV, D)
 
         scale = D ** -0.5
-        is_decode = past_key_value is not None and q_len == 1
         thres = self.gate_thres
         w_l = self.context_norm_local.weight if self.use_context_norm else None
         w_g = self.context_norm_global.weight if self.use_context_norm else None
         eps = self.context_norm_local.variance_epsilon if self.use_context_norm else 0.0
-        gate_flat = gate.reshape(-1).to(torch.bfloat16)
 
         if is_decode:
             if not isinstance(past_key_value, Cache):
@@ -278,12 +299,6 @@ class LoGoAttention(nn.Module):
             self._last_status = st.status
             fused = ops.fuse_norm_blend(local, glob, gate_flat, thres, w_l, w_g, eps, self.use_context_norm)
         else:
-            filled = 0
-            if past_key_value is not None:
-                if not isinstance(past_key_value, Cache):
-                    raise TypeError("the cache must be a logo_b200.Cache")
-                filled = (past_key_value.layers[self.layer_idx].length
-                          if len(past_key_value.layers) > self.layer_idx else 0)
             n = bsz * q_len
             if filled != 0:
                 # several new tokens on top of cached ones (chunked prefill, logo/cache.py:95-118)
@@ -294,11 +309,12 @@ class LoGoAttention(nn.Module):
             else:
                 if past_key_value is not None:
                     past_key_value.append(self.layer_idx, k_l, v_l, k_g, v_g, self.local_window_size, layout="bthd")
-                if cu_seqlens is not None:
-                    cu = cu_seqlens
-                else:  # equal-length batch packed to one varlen batch (logo.py:200-209)
-                    cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
-                sel = ops.select_rows(gate_flat, thres, cu)
+                if sel is None:
+                    if cu_seqlens is not None:
+                        cu = cu_seqlens
+                    else:  # equal-length batch packed to one varlen batch (logo.py:200-209)
+                        cu = torch.arange(0, (bsz + 1) * q_len, q_len, dtype=torch.int32, device=hidden_states.device)
+                    sel = ops.select_rows(gate_flat, thres, cu)
                 local = ops.SWAFunction.apply(q_l.reshape(n, H, D), k_l.reshape(n, HKV, D), v_l.reshape(n, HKV, D),
                                               self.local_window_size, scale, sel)
                 glob = ops.SQFullAttentionFunction.apply(q_g.reshape(1, n, H, D), k_g.reshape(1, n, HKV, D),
@@ -518,12 +534,6 @@ class Attention(nn.Module):
             _, out = decode_attention(qd, qd, st, ones, zero, scale)
             out = out.view(bsz, 1, H * D)
         else:
-            filled = 0
-            if past_key_value is not None:
-                if not isinstance(past_key_value, Cache):
-                    raise TypeError("the cache must be a logo_b200.Cache")
-                filled = (past_key_value.layers[self.layer_idx].length
-                          if len(past_key_value.layers) > self.layer_idx else 0)
             if filled != 0:
                 if cu_seqlens is not None:
                     raise NotImplementedError("a packed batch cannot continue a cache: pass [B, T] inputs")

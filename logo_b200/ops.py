@@ -30,6 +30,7 @@ __all__ = [
     "assert_close",
     "check_device_status",
     "lm_head_cross_entropy",
+    "proj_rope",
 ]
 
 HEAD_DIM = 128
@@ -425,6 +426,62 @@ class RopeFunction(torch.autograd.Function):
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """Rotary embedding of ``x [N, H, 128]`` with per-token tables ``cos, sin [N, 128]`` (all bf16)."""
     return RopeFunction.apply(x, cos, sin)
+
+
+# ----------------------------------------------------------------------------------------
+# per-head projection of the global branch fused with the rotary embedding
+# (logo/layers/logo.py:86-94 + :137-139 + the layout copies of :156-158)
+# ----------------------------------------------------------------------------------------
+class ProjRopeFunction(torch.autograd.Function):
+    """``out[t, h] = rope(x[t, h] @ w[h])`` in one kernel; with a selection only its rows are computed.
+
+    The backward un-rotates the gradient with the rotary kernel and forms the two gradient products
+    with batched GEMMs (rows outside the selection carry a zero gradient: the attention backward
+    writes zeros there)."""
+
+    @staticmethod
+    @_fwd_bf16
+    def forward(ctx, x, w, cos, sin, sel):
+        lib = _lib.load()
+        _require_cuda(x, w, cos, sin)
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise TypeError("proj_rope takes bf16 activations and bf16 per-head weights")
+        n, heads, d = x.shape
+        if x.stride(2) != 1 or x.stride(1) != d or x.stride(0) % 8 or x.data_ptr() % 16:
+            x = x.contiguous()
+        w = w.contiguous()
+        if cos is not None:
+            cos, sin = cos.contiguous(), sin.contiguous()
+        out = torch.empty(n, heads, d, dtype=torch.bfloat16, device=x.device)
+        status = sel.status if sel is not None else torch.zeros(1, dtype=torch.int32, device=x.device)
+        with _lib.on_device(x):
+            rc = lib.logo_proj_rope(x.data_ptr(), x.stride(0), w.data_ptr(),
+                                    sel.q_idx.data_ptr() if sel is not None else None,
+                                    sel.meta.data_ptr() if sel is not None else None, _lib.ptr(cos), _lib.ptr(sin),
+                                    out.data_ptr(), n, heads, d, status.data_ptr(), _lib.current_stream_ptr(x.device))
+        _lib.check(rc, "logo_proj_rope")
+        ctx.save_for_backward(x, w, cos, sin)
+        return out
+
+    @staticmethod
+    @_bwd
+    def backward(ctx, g):
+        x, w, cos, sin = ctx.saved_tensors
+        if cos is not None:
+            g = _rope_call(g, cos, sin, True)
+        else:
+            g = g.contiguous()
+        dx = torch.einsum("l h e, h d e -> l h d", g, w) if ctx.needs_input_grad[0] else None
+        dw = torch.einsum("l h d, l h e -> h d e", x, g) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None, None
+
+
+def proj_rope(x: torch.Tensor, w: torch.Tensor, cos: Optional[torch.Tensor] = None,
+              sin: Optional[torch.Tensor] = None, sel: Optional[SelMeta] = None) -> torch.Tensor:
+    """``x [N, H, 128]`` (rows of a token contiguous), ``w [H, 128, 128]``, ``cos / sin [N, 128]`` or None;
+    returns ``[N, H, 128]`` bf16. With ``sel`` only the selected token rows are computed; the others
+    are left unwritten (the query-sparse attention never reads them)."""
+    return ProjRopeFunction.apply(x, w, cos, sin, sel)
 
 
 # ----------------------------------------------------------------------------------------

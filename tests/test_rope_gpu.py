@@ -103,3 +103,54 @@ def test_rope_against_reference_fixture(cuda_device, golden):
     out.backward(torch.from_numpy(grad_out).to(torch.bfloat16).to(cuda_device))
     np.testing.assert_array_equal(out.detach().float().cpu().numpy(), g["out"])
     np.testing.assert_array_equal(xd.grad.float().cpu().numpy(), g["grad"])
+
+
+@pytest.mark.parametrize("with_rows,with_rope", [(False, True), (True, True), (False, False)])
+def test_proj_rope_matches_the_eager_bf16_graph(cuda_device, with_rows, with_rope):
+    """Per-head projection + rotary embedding in one kernel against the eager bf16 expressions it replaces
+    (the einsum of logo/layers/logo.py:86-94 followed by apply_rotary_pos_emb): same roundings, so the
+    results agree except where the two fp32 accumulation orders of the product round to neighbouring
+    bf16 values. Forward and the gradients of x and w."""
+    from logo_b200 import ops
+
+    torch.manual_seed(5)
+    n, heads, d = 700, 3, 128
+    x = torch.randn(n, heads * d, device=cuda_device).to(torch.bfloat16)
+    w = (torch.eye(d, device=cuda_device)[None] + 0.05 * torch.randn(heads, d, d, device=cuda_device)).to(torch.bfloat16)
+    pos = torch.arange(n, device=cuda_device).float()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, device=cuda_device).float() / d))
+    emb = torch.cat([pos[:, None] * inv[None], pos[:, None] * inv[None]], dim=-1)
+    cos, sin = (emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)) if with_rope else (None, None)
+    sel = None
+    keep = torch.ones(n, dtype=torch.bool, device=cuda_device)
+    if with_rows:
+        keep = torch.rand(n, device=cuda_device) < 0.4
+        sel = ops.select_rows(keep, None, torch.tensor([0, 300, 300, n], dtype=torch.int32, device=cuda_device))
+    g_out = torch.randn(n, heads, d, device=cuda_device).to(torch.bfloat16) * keep[:, None, None]
+
+    def eager(xr, wr):
+        y = torch.einsum("l h d, h d e -> l h e", xr.view(n, heads, d), wr)
+        if cos is None:
+            return y
+        rot = torch.cat((-y[..., d // 2:], y[..., : d // 2]), dim=-1)
+        return (y * cos[:, None, :]) + (rot * sin[:, None, :])
+
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ref = eager(xr, wr)
+    ref.backward(g_out)
+    xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    out = ops.proj_rope(xd.view(n, heads, d), wd, cos, sin, sel)
+    out.backward(g_out)
+    torch.cuda.synchronize()
+    if sel is not None:
+        assert int(sel.status.item()) == 0
+    got, want = out[keep].float(), ref.detach()[keep].float()
+    ulp = want.abs().clamp_min(2.0 ** -126) * 2.0 ** -7
+    assert torch.all((got - want).abs() <= 2 * ulp + 1e-3)       # neighbouring bf16 values at most, rotation included
+    assert (got != want).float().mean().item() < 0.05
+    assert oracle_err(xr.grad.float(), xd.grad.float()) < 1e-2
+    assert oracle_err(wr.grad.float(), wd.grad.float()) < 1e-2
+
+
+def oracle_err(ref, got):
+    return ((ref - got).square().mean().sqrt() / (ref.square().mean().sqrt() + 1e-8)).item()
