@@ -152,46 +152,28 @@ __device__ __forceinline__ void dq_decode_item(const BwdArgs& a, int w, int tota
   }
 }
 
-// Shared memory (all dynamic): the Q / dO tiles of the item, two K stages, two V stages, and one tile
-// DSB that carries dS (bf16, [query][key]) from the element-wise warps to the dQ product. With dS in
-// shared memory instead of on top of dP in tensor memory, dP of the next key tile is formed as soon
-// as the warps hold this tile's dP in registers, instead of behind the dQ product that reads dS.
-struct DqSmem {
-  static constexpr uint32_t Q = 0, DO = TILE_BYTES, K = 2 * TILE_BYTES, V = 4 * TILE_BYTES, DSB = 6 * TILE_BYTES;
-  static constexpr uint32_t BARS = 7 * TILE_BYTES;
-  static constexpr uint32_t N_BARS = 18 + 2 * ITEM_RING;
-  static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
-  static constexpr uint32_t MISC = ITEMS + ITEM_RING * ITEM_WORDS * 4;
-  static constexpr uint32_t BYTES = MISC + 16;
-};
-static_assert(DqSmem::BYTES <= 232448, "the dQ kernel does not fit the 227 KB of shared memory");
-
 __global__ void __launch_bounds__(DQ_THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                        const BwdArgs a) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sQ = smem + DqSmem::Q;
-  uint8_t* sDO = smem + DqSmem::DO;
-  uint8_t* sK = smem + DqSmem::K;     // 2 stages
-  uint8_t* sV = smem + DqSmem::V;     // 2 stages
-  uint8_t* sDS = smem + DqSmem::DSB;  // dS of the step; at the end of an item the staging of the dQ stores
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DqSmem::BARS);
-  uint64_t &qdo_full = bars[0], &qdo_free = bars[1], *k_full = bars + 2, *k_empty = bars + 4, *v_full = bars + 6,
-           *v_empty = bars + 8, *s_full = bars + 10, &dp_full = bars[12], &dp_read = bars[13], &ds_ready = bars[14],
-           &dq_done = bars[15], &acc_done = bars[16];
-  const ItemRing ring{reinterpret_cast<int*>(smem + DqSmem::ITEMS), bars + 18, bars + 18 + ITEM_RING};
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + DqSmem::MISC);
-  int& abort_flag = *reinterpret_cast<int*>(smem + DqSmem::MISC + 4);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* sV = smem + 4 * TILE_BYTES;   // 2 stages
+
+  __shared__ uint64_t qdo_full, qdo_free, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ uint64_t s_full[2], dp_full, ds_ready, acc_done;
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
-
-  // the tile layouts (TMA 128-byte swizzle, UMMA descriptors) assume a 1024-byte aligned base
-  if ((smem_u32(smem) & 1023u) != 0u) {
-    if (tid == 0 && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
-    return;
-  }
 
   if (tid == 0) {
     abort_flag = 0;
@@ -205,9 +187,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
       mbar_init(&s_full[s], 1);
     }
     mbar_init(&dp_full, 1);
-    mbar_init(&dp_read, DQ_EW_WARPS);    // one arrival per warp
-    mbar_init(&ds_ready, DQ_EW_WARPS);
-    mbar_init(&dq_done, 1);
+    mbar_init(&ds_ready, DQ_EW_WARPS);   // one arrival per warp
     mbar_init(&acc_done, 1);
     ring_init(ring, DQ_EW_WARPS + 1);
     fence_barrier_init();
@@ -235,9 +215,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const int col0 = part * 32;
     const float c = a.scale_log2;
-    // this thread's 64 bytes of the dS tile: row `row` of block part / 2, chunks 4 * (part % 2) .. + 3
-    uint8_t* ds_row = sDS + (uint32_t)(part >> 1) * BLK_BYTES + (uint32_t)row * 128u;
-    const uint32_t ch0 = (uint32_t)(part & 1) * 4u;
     uint32_t idx = 0;      // key steps processed so far (all items)
     uint32_t n_items = 0;
 
@@ -274,22 +251,17 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
           uint32_t d0[32];
           tmem_ld32(TM_DP + lane_off + (uint32_t)col0, d0);
           tmem_ld_wait();
-          tc_fence_before();
-          mbar_arrive_warp(&dp_read);    // the dP columns may take the next key tile's product
           ds_pack_chunk_row(p0, d0, delta_r, pk);
         }
-        // dS goes to DSB as a [query][key] tile (two [128][64] blocks, 128-byte swizzled) once the dQ
-        // product of the previous step has read the previous one
-        if (idx > 0) mbar_wait(&dq_done, (idx - 1u) & 1u, ab);
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(ds_row + (((ch0 + (uint32_t)ch) ^ ((uint32_t)row & 7u)) << 4)) =
-              make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-        fence_proxy_async_smem();
+        // dS (bf16) goes into the first 16 of the 32 dP columns this warp has just read: no other warp
+        // reads or writes them, so no barrier is needed before the overwrite
+        tmem_st16(TM_DP + lane_off + (uint32_t)col0, pk);
+        tmem_st_wait();
+        tc_fence_before();
         mbar_arrive_warp(&ds_ready);
       }
 
-      // ---- epilogue: dQ * scale -> bf16 rows (staged through DSB: every product of the item has completed) ----
+      // ---- epilogue: dQ * scale -> bf16 rows ----
       mbar_wait(&acc_done, n_items & 1u, ab);
       tc_fence_after();
       ++n_items;
@@ -305,11 +277,12 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * a.scale, __uint_as_float(r[2 * i + 1]) * a.scale);
-        store_patch_32x32(sDS + warp * 2048, pk, a.dq, row_off, lane);
+        // eight staging buffers for sixteen warps: two rounds
+        if (part < 2) store_patch_32x32(s_stage[warp], pk, a.dq, row_off, lane);
+        named_barrier_sync(1, DQ_EW_WARPS * 32);
+        if (part >= 2) store_patch_32x32(s_stage[warp - 8], pk, a.dq, row_off, lane);
       }
       tc_fence_before();
-      // DSB is the next item's dS tile: no warp may write it while another still stages its stores
-      named_barrier_sync(1, DQ_EW_WARPS * 32);
       ring_release(ring, n_ring);
     }
   } else if (warp == DQ_EW_WARPS) {
@@ -371,18 +344,16 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
     {   // MMA issuer: the whole warp walks this code, an elected lane issues (see umma_ss)
       const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);       // both operands K-major
       const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);   // B operand MN-major
-      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), k_base = smem_u32(sK), v_base = smem_u32(sV),
-                     ds_base = smem_u32(sDS);
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), k_base = smem_u32(sK), v_base = smem_u32(sV);
       uint32_t kv_iter = 0, n_items = 0;
 
       auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
         umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
                                      idesc_kk, 0u);
       };
-      // dQ += dS K: A = the dS tile in shared memory (K-major), B = the K tile read MN-major
-      auto issue_dq = [&](uint32_t b_base, bool acc) {
-        umma_tile_k128<false, true>(TM_DQ, umma_desc_sw128(ds_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
-                                    idesc_mn, acc ? 1u : 0u);
+      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
+        umma_tile_k128<true, true, 4>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+                                      acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
@@ -396,9 +367,9 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
         mbar_wait(&qdo_full, n_items & 1u, ab);
         ++n_items;
         tc_fence_after();
-        // Issue order. The scores run two key tiles ahead into the S buffer the warps finished reading a
-        // step earlier; dP of the next key tile goes out the moment the warps hold this tile's dP in
-        // registers; dQ(j) follows dS(j).
+        // Issue order. dQ(j) and dP(j+1) go out the moment dS(j) is ready (they are the dependency
+        // chain of the element-wise warps); the scores run two key tiles ahead into the S buffer the
+        // warps finished reading a step earlier, so a K tile that is still in flight delays nothing.
         const int n_kt = it.je - it.jb;
         {
           const uint32_t st = kv_iter & 1u, ph = (kv_iter >> 1) & 1u;
@@ -424,7 +395,10 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
           const uint32_t nx = kv_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
           const uint32_t nx2 = kv_iter + 2u, ph_n2 = (nx2 >> 1) & 1u;   // same stage / S buffer as step j
           const bool has_next = (j + 1 < it.je), has_next2 = (j + 2 < it.je);
-          mbar_wait(&dp_read, kv_iter & 1u, ab);
+          mbar_wait(&ds_ready, kv_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DQ, TM_DP, k_base + st * TILE_BYTES, j > it.jb);
+          umma_commit(&k_empty[st]);
           if (has_next) {
             mbar_wait(&v_full[st_n], ph_n, ab);
             tc_fence_after();
@@ -432,11 +406,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
             umma_commit(&dp_full);
             umma_commit(&v_empty[st_n]);
           }
-          mbar_wait(&ds_ready, kv_iter & 1u, ab);
-          tc_fence_after();
-          issue_dq(k_base + st * TILE_BYTES, j > it.jb);
-          umma_commit(&dq_done);        // DSB may take the next dS
-          umma_commit(&k_empty[st]);
           if (has_next2) {
             mbar_wait(&k_full[st], ph_n2, ab);
             tc_fence_after();
@@ -461,53 +430,31 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
 // ---------------------------------------------------------------------------------------
 // 3. dK / dV
 // ---------------------------------------------------------------------------------------
-// Shared memory (all dynamic): K, V, two Q stages, two dO stages, and one tile PB that carries
-// P^T (bf16, [key][query]) from the element-wise warps to the dV product. With P^T in shared
-// memory instead of on top of S^T in tensor memory, the S^T columns are free again as soon as the
-// warps hold the scores in registers, so the scores of the NEXT query tile are formed while the
-// warps still exponentiate this one: the chain S^T -> P^T -> dV -> next S^T that paced the kernel
-// (2700 of 3460 clocks per step) is gone. dS^T still overwrites dP^T in tensor memory and is the
-// TMEM A operand of dK; the tensor pipe itself orders dK(s) before dP^T(s + 1).
-struct DkvSmem {
-  static constexpr uint32_t K = 0, V = TILE_BYTES, Q = 2 * TILE_BYTES, DO = 4 * TILE_BYTES, PB = 6 * TILE_BYTES;
-  static constexpr uint32_t LSE = 7 * TILE_BYTES, DELTA = LSE + TILE * 4, POS = DELTA + TILE * 4;
-  static constexpr uint32_t BARS = POS + TILE * 4;
-  static constexpr uint32_t N_BARS = 17 + 2 * ITEM_RING;
-  static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
-  static constexpr uint32_t MISC = ITEMS + ITEM_RING * ITEM_WORDS * 4;
-  static constexpr uint32_t BYTES = MISC + 16;
-};
-static_assert(DkvSmem::BYTES <= 232448, "the dK/dV kernel does not fit the 227 KB of shared memory");
-
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const BwdArgs a) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sK = smem + DkvSmem::K;
-  uint8_t* sV = smem + DkvSmem::V;
-  uint8_t* sQ = smem + DkvSmem::Q;      // 2 stages
-  uint8_t* sDO = smem + DkvSmem::DO;    // 2 stages
-  uint8_t* sPB = smem + DkvSmem::PB;    // P^T of the step; at the end of an item the staging of the stores
-  float* s_lse = reinterpret_cast<float*>(smem + DkvSmem::LSE);
-  float* s_delta = reinterpret_cast<float*>(smem + DkvSmem::DELTA);
-  int* s_pos = reinterpret_cast<int*>(smem + DkvSmem::POS);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkvSmem::BARS);
-  uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
-           *do_empty = bars + 8, &st_full = bars[10], &dpt_full = bars[11], &s_read = bars[12], &p_ready = bars[13],
-           &dv_done = bars[14], &ds_ready = bars[15], &acc_done = bars[16];
-  const ItemRing ring{reinterpret_cast<int*>(smem + DkvSmem::ITEMS), bars + 17, bars + 17 + ITEM_RING};
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + DkvSmem::MISC);
-  int& abort_flag = *reinterpret_cast<int*>(smem + DkvSmem::MISC + 4);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;    // 2 stages
+  uint8_t* sDO = smem + 4 * TILE_BYTES;   // 2 stages
+
+  __shared__ uint64_t kv_full, kv_free, q_full[2], q_empty[2], do_full[2], do_empty[2];
+  __shared__ uint64_t st_full, dpt_full, p_ready, ds_ready, acc_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) float s_lse[2][TILE];
+  __shared__ __align__(16) float s_delta[2][TILE];
+  __shared__ __align__(16) int s_pos[2][TILE];
+  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
+  __shared__ int s_items[ITEM_RING * ITEM_WORDS];
+  __shared__ uint64_t item_full[ITEM_RING], item_empty[ITEM_RING];
+  const ItemRing ring{s_items, item_full, item_empty};
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   AbortState ab{&abort_flag, a.status};
-
-  // the tile layouts (TMA 128-byte swizzle, UMMA descriptors) assume a 1024-byte aligned base
-  if ((smem_u32(smem) & 1023u) != 0u) {
-    if (tid == 0 && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
-    return;
-  }
 
   if (tid == 0) {
     abort_flag = 0;
@@ -521,9 +468,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
     mbar_init(&st_full, 1);
     mbar_init(&dpt_full, 1);
-    mbar_init(&s_read, 8);     // one arrival per warp
-    mbar_init(&p_ready, 8);
-    mbar_init(&dv_done, 1);
+    mbar_init(&p_ready, 8);    // one arrival per warp
     mbar_init(&ds_ready, 8);
     mbar_init(&acc_done, 1);
     ring_init(ring, 9);
@@ -551,28 +496,27 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const float c = a.scale_log2;
     uint32_t idx = 0, n_items = 0;
 
-    // lse / delta / pos of row `tid` of query tile `i` of head `hq`: loaded unconditionally from a
-    // clamped row into registers (threads 0-127), stored to the shared vectors between two steps
-    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
-      const int r = i * TILE + (tid & (TILE - 1));
+    // Loads lse / delta / pos of query tile `i` of head `hq` into registers. The loads are issued
+    // unconditionally from a clamped row (no select on a loaded value before it is needed, which
+    // would expose the memory round trip); rows past the end are replaced when the values are used.
+    const int vrow = tid & (TILE - 1);
+    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) -> bool {
+      const int r = i * TILE + vrow;
       const int rc = min(r, it.nsel - 1);
       const size_t sidx = (size_t)hq * a.cap + it.bos_q + rc;
       l = __ldg(a.lse_sel + sidx);
       d = __ldg(a.delta_sel + sidx);
       p = bwd_row_position(a, it.bos_q, rc);
-      if (r >= it.nsel) {   // rows past the end of the sequence see no key
-        l = 0.f;
-        d = 0.f;
-        p = -1;
-      }
+      return r < it.nsel;
     };
 
     // Items are walked one ahead: during the last step of an item the next record is popped and its
-    // first-step vectors are fetched, so the next item begins without a memory round trip.
+    // first-step vectors start travelling to shared memory, so the next item begins without a
+    // memory round trip.
     uint32_t n_ring = 0;
     DkvItem it;
     long long w = ring_pop(ring, n_ring, it, ab);
-    bool vec_ready = false;   // the first-step vectors of `it` are already in the shared vectors
+    bool vec_ready = false;   // the first-step vectors of `it` are already in s_*[idx & 1]
     while (w >= 0) {
       DkvItem it_next;
       long long w_next = -1;
@@ -580,11 +524,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const int nq = it.i_end - it.i0;
       const int key_pos = it.kv_start + row;
       const bool key_valid = key_pos < it.len_k;
+      __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
+      __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + (key_valid ? key_pos : 0)) * a.h + it.kvh) * HEAD_DIM + col0;
       if (nq <= 0) {
         // no query can see this key tile: the gradients are zero
         if (key_valid) {
-          __nv_bfloat16* dk_row = a.dk + ((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0;
-          __nv_bfloat16* dv_row = a.dv + ((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             reinterpret_cast<uint4*>(dk_row)[g] = make_uint4(0, 0, 0, 0);
@@ -602,14 +546,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const int n_steps = nq * G;
       const bool partial_keys = it.kv_start + TILE > it.len_k;
 
+      // vectors of the first step, unless the previous item already fetched them
       if (!vec_ready) {
+        float l, d;
+        int p;
+        const bool ok = fetch_vec(it, it.kvh * G, it.i0, l, d, p);
         if (tid < TILE) {
-          float l, d;
-          int p;
-          fetch_vec(it, it.kvh * G, it.i0, l, d, p);
-          s_lse[tid] = l;
-          s_delta[tid] = d;
-          s_pos[tid] = p;
+          s_lse[idx & 1u][tid] = ok ? l : 0.f;
+          s_delta[idx & 1u][tid] = ok ? d : 0.f;
+          s_pos[idx & 1u][tid] = ok ? p : -1;
         }
         named_barrier_sync(3, 256);
       }
@@ -620,20 +565,30 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           i_nx = 0;
           ++g_nx;
         }
-        // the vectors of the next step (of the next item after the last step) start travelling now
+        const uint32_t vb = idx & 1u;
+        // prefetch the vectors of the next step
+        // the vectors of the next step travel global -> shared asynchronously (the buffer they land
+        // in was last read before barrier 2 of the previous step)
         const bool has_next = (s + 1 < n_steps);
+        bool next_ok = true;
         if (!has_next) {
           w_next = ring_pop(ring, n_ring + 1, it_next, ab);
           vec_next = (w_next >= 0) && (it_next.i_end > it_next.i0);
         }
-        float l_nx = 0.f, d_nx = 0.f;
-        int p_nx = -1;
         if ((has_next || vec_next) && tid < TILE) {
-          if (has_next) fetch_vec(it, it.kvh * G + g_nx, it.i0 + i_nx, l_nx, d_nx, p_nx);
-          else fetch_vec(it_next, it_next.kvh * G, it_next.i0, l_nx, d_nx, p_nx);
+          const DkvItem& src = has_next ? it : it_next;
+          const int hq_nx = src.kvh * G + (has_next ? g_nx : 0);
+          const int r = (src.i0 + (has_next ? i_nx : 0)) * TILE + tid;
+          const int rc = min(r, src.nsel - 1);
+          next_ok = r < src.nsel;
+          const size_t sidx = (size_t)hq_nx * a.cap + src.bos_q + rc;
+          cp_async_4(&s_lse[vb ^ 1u][tid], a.lse_sel + sidx);
+          cp_async_4(&s_delta[vb ^ 1u][tid], a.delta_sel + sidx);
+          if (a.q_idx) cp_async_4(&s_pos[vb ^ 1u][tid], a.pos_ids + src.bos_q + rc);
+          else s_pos[vb ^ 1u][tid] = next_ok ? r : -1;
         }
 
-        const int pos_first = s_pos[0], pos_last = s_pos[TILE - 1];
+        const int pos_first = s_pos[vb][0], pos_last = s_pos[vb][TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
                             (a.window > 0 && pos_last > it.kv_start + a.window);
         uint32_t p0[32], p1[32];
@@ -642,23 +597,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tmem_ld32(TM_ST + lane_off + (uint32_t)col0, p0);
         tmem_ld32(TM_ST + lane_off + (uint32_t)col0 + 32, p1);
         tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive_warp(&s_read);    // the S^T columns may take the scores of the next query tile
-        prob_chunk_col(p0, c, &s_lse[col0], &s_pos[col0], masked, key_valid, key_pos, a.window);
-        prob_chunk_col(p1, c, &s_lse[col0 + 32], &s_pos[col0 + 32], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p0, c, &s_lse[vb][col0], &s_pos[vb][col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_col(p1, c, &s_lse[vb][col0 + 32], &s_pos[vb][col0 + 32], masked, key_valid, key_pos, a.window);
         {
           uint32_t pk[32];
           pack_chunk(p0, pk);
           pack_chunk(p1, pk + 16);
-          // P^T goes to PB as a [key][query] tile (two [128][64] blocks, 128-byte swizzled) once dV of the
-          // previous step has read the previous one
-          if (idx > 0) mbar_wait(&dv_done, (idx - 1u) & 1u, ab);
-          uint8_t* dst = sPB + (uint32_t)half * BLK_BYTES + (uint32_t)row * 128u;
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch)
-            *reinterpret_cast<uint4*>(dst + (((uint32_t)ch ^ ((uint32_t)row & 7u)) << 4)) =
-                make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-          fence_proxy_async_smem();
+          // P^T (bf16) overwrites the first 32 of the 64 S^T columns this warp has just read: private
+          // to the warp, no barrier needed
+          tmem_st32(TM_ST + lane_off + (uint32_t)col0, pk);
+          tmem_st_wait();
+          tc_fence_before();
           mbar_arrive_warp(&p_ready);
         }
         mbar_wait(&dpt_full, idx & 1u, ab);
@@ -670,33 +619,28 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             tmem_ld32(TM_DPT + lane_off + (uint32_t)col0, d0);
             tmem_ld32(TM_DPT + lane_off + (uint32_t)col0 + 32, d1);
             tmem_ld_wait();
-            ds_pack_chunk_col(p0, d0, &s_delta[col0], pk);
-            ds_pack_chunk_col(p1, d1, &s_delta[col0 + 32], pk + 16);
+            ds_pack_chunk_col(p0, d0, &s_delta[vb][col0], pk);
+            ds_pack_chunk_col(p1, d1, &s_delta[vb][col0 + 32], pk + 16);
           }
-          // dS^T (bf16) overwrites the first 32 of the 64 dP^T columns this warp has just read
+          if ((has_next || vec_next) && tid < TILE) {
+            cp_async_wait_all();
+            if (!next_ok) s_pos[vb ^ 1u][tid] = -1;   // rows past the end of the sequence see no key
+          }
+          named_barrier_sync(2, 256);   // vector buffers: this step.s reads done, next step.s values visible
           tmem_st32(TM_DPT + lane_off + (uint32_t)col0, pk);
           tmem_st_wait();
           tc_fence_before();
           mbar_arrive_warp(&ds_ready);
         }
-        // hand the vectors over: every warp has finished reading this step's, then the next step's land
-        named_barrier_sync(2, 256);
-        if ((has_next || vec_next) && tid < TILE) {
-          s_lse[tid] = l_nx;
-          s_delta[tid] = d_nx;
-          s_pos[tid] = p_nx;
-        }
-        named_barrier_sync(3, 256);
       }
 
-      // ---- epilogue (the stores are staged through PB: every product of the item has completed) ----
+      // ---- epilogue ----
       mbar_wait(&acc_done, n_items & 1u, ab);
       tc_fence_after();
       ++n_items;
       {
         const long long row_off =
             key_valid ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0) : -1;
-        uint8_t* stage = sPB + warp * 2048;
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
@@ -709,13 +653,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
-            store_patch_32x32(stage, pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+            store_patch_32x32(s_stage[warp], pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
           }
         }
       }
       tc_fence_before();
-      // PB is the next item's P^T tile: no warp may write it while another still stages its stores
-      named_barrier_sync(2, 256);
       ring_release(ring, n_ring);
       it = it_next;
       w = w_next;
@@ -786,22 +728,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     {   // MMA issuer: the whole warp walks this code, an elected lane issues (see umma_ss)
       const uint32_t idesc_kk = umma_idesc_bf16(TILE, TILE, 0, 0);
       const uint32_t idesc_mn = umma_idesc_bf16(TILE, HEAD_DIM, 0, 1);
-      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO),
-                     pb_base = smem_u32(sPB);
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
       uint32_t q_iter = 0, n_items = 0;
 
       auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
         umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
                                      idesc_kk, 0u);
       };
-      // dV += P^T dO: A = the P^T tile in shared memory (K-major), B = the dO tile read MN-major
-      auto issue_dv = [&](uint32_t b_base, bool acc) {
-        umma_tile_k128<false, true>(TM_DV, umma_desc_sw128(pb_base, 0, 1024), umma_desc_sw128(b_base, BLK_BYTES, 1024),
-                                    idesc_mn, acc ? 1u : 0u);
-      };
-      // dK += dS^T Q: A = dS^T in tensor memory, B = the Q tile read MN-major
-      auto issue_dk = [&](uint32_t b_base, bool acc) {
-        umma_tile_k128<true, true, 2>(TM_DK, TM_DPT, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
+      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool acc) {
+        umma_tile_k128<true, true, 2>(d_tmem, a_tmem, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn,
+                                         acc ? 1u : 0u);
       };
 
       for (uint32_t n_ring = 0;; ++n_ring) {
@@ -832,28 +768,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           const uint32_t st = q_iter & 1u;
           const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
           const bool has_next = (s + 1 < n_steps);
-          // the scores of the next query tile as soon as the warps hold this tile's in registers
-          mbar_wait(&s_read, q_iter & 1u, ab);
+          // every product that reads K / V has been issued: the next item's tiles may come in while
+          // this item's last two accumulations and its epilogue run
+          if (!has_next) umma_commit(&kv_free);
+          mbar_wait(&p_ready, q_iter & 1u, ab);
+          tc_fence_after();
+          issue_ts(TM_DV, TM_ST, do_base + st * TILE_BYTES, s > 0);
+          umma_commit(&do_empty[st]);
           if (has_next) {
             mbar_wait(&q_full[st_n], ph_n, ab);
             tc_fence_after();
             issue_kk(TM_ST, k_base, q_base + st_n * TILE_BYTES);
             umma_commit(&st_full);
           }
-          mbar_wait(&p_ready, q_iter & 1u, ab);
-          tc_fence_after();
-          issue_dv(do_base + st * TILE_BYTES, s > 0);
-          umma_commit(&dv_done);        // PB may take the next P^T
-          umma_commit(&do_empty[st]);
           mbar_wait(&ds_ready, q_iter & 1u, ab);
           tc_fence_after();
-          issue_dk(q_base + st * TILE_BYTES, s > 0);
+          issue_ts(TM_DK, TM_DPT, q_base + st * TILE_BYTES, s > 0);
           umma_commit(&q_empty[st]);
-          // every product that reads K / V has been issued: the next item's tiles may come in while
-          // this item's epilogue runs
-          if (!has_next) umma_commit(&kv_free);
           if (has_next) {
-            // ordered behind dK(s) by the tensor pipe: dS^T in the dP^T columns has been consumed
             mbar_wait(&do_full[st_n], ph_n, ab);
             tc_fence_after();
             issue_kk(TM_DPT, v_base, do_base + st_n * TILE_BYTES);
@@ -983,19 +915,19 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   LOGO_CHECK_CUDA(cudaGetDevice(&dev));
   if (attr_set_dev != dev) {
     LOGO_CHECK_CUDA(
-        cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DqSmem::BYTES));
+        cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
     LOGO_CHECK_CUDA(
-        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DkvSmem::BYTES));
+        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES));
     attr_set_dev = dev;
   }
   LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dq, 0, sizeof(int), stream));
   LOGO_CHECK_CUDA(cudaMemsetAsync(counter_dkv, 0, sizeof(int), stream));
   prof_begin(PROF_BWD_DKV, stream);
-  attn_bwd_dkv_kernel<<<sms, BWD_THREADS, DkvSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  attn_bwd_dkv_kernel<<<sms, BWD_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
   prof_end(PROF_BWD_DKV, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_DQ, stream);
-  attn_bwd_dq_kernel<<<sms, DQ_THREADS, DqSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
+  attn_bwd_dq_kernel<<<sms, DQ_THREADS, BWD_SMEM_BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, a);
   prof_end(PROF_BWD_DQ, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;

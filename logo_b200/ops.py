@@ -593,7 +593,7 @@ class LmHeadLossFunction(torch.autograd.Function):
                     d_weight += (logits.t() @ hidden[a:b]).float()
         ctx.save_for_backward(d_hidden, d_weight.to(weight.dtype) if need_w else None)
         ctx.status = status
-        return row_loss.sum() / n_valid.clamp(min=1).to(torch.float32)
+        return (row_loss.sum() / n_valid.clamp(min=1).to(torch.float32)).reshape(())
 
     @staticmethod
     @_bwd
