@@ -534,6 +534,12 @@ class Attention(nn.Module):
             _, out = decode_attention(qd, qd, st, ones, zero, scale)
             out = out.view(bsz, 1, H * D)
         else:
+            filled = 0
+            if past_key_value is not None:
+                if not isinstance(past_key_value, Cache):
+                    raise TypeError("the cache must be a logo_b200.Cache")
+                filled = (past_key_value.layers[self.layer_idx].length
+                          if len(past_key_value.layers) > self.layer_idx else 0)
             if filled != 0:
                 if cu_seqlens is not None:
                     raise NotImplementedError("a packed batch cannot continue a cache: pass [B, T] inputs")

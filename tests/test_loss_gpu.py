@@ -30,7 +30,8 @@ def test_lm_head_cross_entropy_vs_oracle(cuda_device, name, shape, vocab, cu, ch
     hidden, weight, labels, cu = _case(shape, vocab, hid, cu, seed=len(name))
     hr, wr = hidden.float().requires_grad_(True), weight.float().requires_grad_(True)
     # the oracle sees the logits the bf16 lm_head produces (the reference upcasts AFTER the bf16 linear)
-    logits = (hr @ wr.t()).to(torch.bfloat16).float() + ((hr @ wr.t()) - (hr @ wr.t()).detach())
+    exact = hr @ wr.t()
+    logits = exact + (exact.to(torch.bfloat16).float() - exact).detach()
     ref = orc.lm_loss_ref(logits, labels, cu)
     ref.backward()
 
