@@ -323,6 +323,7 @@ def run_gpu(args):
     torch.cuda.empty_cache()
     legs = {} if args.no_legs else run_legs(ctx, args)
     if rank != 0:
+        ctx.barrier()     # rank 0 still runs its single-rank extras; every rank leaves the group together
         ctx.close()
         return
 
@@ -400,7 +401,8 @@ def run_gpu(args):
                                    f"({cpu_ms:.0f} ms each)"},
     }
     line.update(legs)
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
+    ctx.barrier()
     ctx.close()
 
 
@@ -761,7 +763,9 @@ def run_one_leg(args):
         print(json.dumps({"metric": metric, "value": res[key], "unit": unit, "n_gpus": ctx.world, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": res.get("ms_per_step", res.get("fwd_ms")),
                           "higher_is_better": True, "scaling": scaling, "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": fn.__doc__.split("\n\n")[0].replace("\n    ", " ")}, "detail": res}))
+                          "config": {"workload": fn.__doc__.split("\n\n")[0].replace("\n    ", " ")}, "detail": res}),
+              flush=True)
+    ctx.barrier()
     ctx.close()
 
 
@@ -968,7 +972,7 @@ def run_reference(args):
                          "sample": "each step = oracle fwd+bwd on 1 sequence x 2048 tokens x 4 heads, fp32"},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
 
 
 def main():
