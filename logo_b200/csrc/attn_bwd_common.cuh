@@ -35,10 +35,6 @@ constexpr int DQ_EW_WARPS = 16;        // dQ kernel: 16 element-wise warps (four
 constexpr int DQ_THREADS = (DQ_EW_WARPS + 2) * 32;
 constexpr int BWD_SMEM_BYTES = 6 * TILE_BYTES + 1024;
 
-__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 __device__ __forceinline__ int bwd_row_position(const BwdArgs& a, int bos_q, int r) {
   return a.q_idx ? __ldg(a.pos_ids + bos_q + r) : r;
 }

@@ -6,13 +6,20 @@
 //
 // A work item is a pair of query tiles (2 x 128 compacted rows of one sequence and one head);
 // the kernel is persistent (one CTA per SM claims items from a global counter through the record
-// ring of attn_common.cuh). Ten warps:
-//   warps 0-3 / 4-7 : softmax groups for query tile 0 / 1 (one thread per row)
-//   warp 8          : claims / decodes items, TMA producer of the 128-key K and V tiles (2-stage rings)
-//   warp 9          : issues tcgen05.mma (whole warp walks the loop, an elected lane issues)
+// ring of attn_common.cuh). Eighteen warps:
+//   warps 0-7 / 8-15 : softmax groups for query tile 0 / 1, two threads per row: warps 0-3 (8-11) take
+//                      keys 0-63 of the score tile and output columns 0-63, warps 4-7 (12-15) the other
+//                      half; the two threads of a row exchange their maxima through shared memory
+//   warp 16          : claims / decodes items, TMA producer of the 128-key K and V tiles (2-stage rings)
+//   warp 17          : issues tcgen05.mma (whole warp walks the loop, an elected lane issues)
+// A tile's softmax sits on the chain scores -> softmax -> P*V -> next scores (P overwrites S); with one
+// thread per row that step took about 2500 clocks against 1024 clocks of tensor-pipe work per tile, so
+// the tiles' softmax phases overlapped and shared the special-function unit. Halving the row work per
+// thread shortens the chain.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each. The bf16
-// probabilities overwrite the first 64 columns of their S buffer and are the A operand of
-// the P*V product straight from tensor memory; V is consumed as an MN-major B operand so
+// probabilities of each column half overwrite the first 32 columns of that half's scores (so the
+// two threads of a row never touch each other's columns) and are the A operand of the P*V
+// product straight from tensor memory; V is consumed as an MN-major B operand so
 // the [keys][128] tile is used as it lies in memory.
 // Softmax runs in base 2 with a lazily updated row maximum: the running maximum is only
 // raised (and O rescaled in tensor memory) when a row's new maximum exceeds it by more
@@ -24,7 +31,8 @@
 
 namespace logo {
 
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_SM_WARPS = 16;   // softmax warps: 2 tiles x 2 column halves x 4 row quarters
+constexpr int FWD_THREADS = (FWD_SM_WARPS + 2) * 32;
 constexpr int FWD_STAGES = 2;
 constexpr int FWD_SMEM_BYTES = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -120,37 +128,58 @@ __device__ __forceinline__ void exp_pack_chunk(const uint32_t (&r)[32], float c,
   }
 }
 
-// One softmax group (128 threads, `row` = thread index inside it) copies the query rows of its
-// tile into 128-byte swizzled shared memory. All sixteen index loads, then all sixteen row loads,
+// One softmax group (256 threads, `idx` = thread index inside it) copies the query rows of its
+// tile into 128-byte swizzled shared memory. All eight index loads, then all eight row loads,
 // are issued back to back (no branch between them), so the copy costs two memory round trips.
-__device__ __forceinline__ void gather_query_tile(const AttnArgs& a, const FwdItem& it, int t, int row, uint8_t* sQt) {
+__device__ __forceinline__ void gather_query_tile(const AttnArgs& a, const FwdItem& it, int t, int idx, uint8_t* sQt) {
   const int nrows = it.nrows[t];
   const int r_base = it.row0 + t * TILE;
-  const int ch = row & 15;  // 16-byte chunk of the 256-byte row
-  uint32_t tok[16];   // token indices fit 31 bits (n_tokens is an int)
+  const int ch = idx & 15;  // 16-byte chunk of the 256-byte row
+  uint32_t tok[8];   // token indices fit 31 bits (n_tokens is an int)
   uint32_t ok_mask = 0;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int r = i * 8 + (row >> 4);
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 16 + (idx >> 4);
     const long long tk = row_token(a, it.bos_q, it.bos_k, r_base + min(r, nrows - 1));
     const bool ok = tk >= 0 && tk < a.n_tokens;
     ok_mask |= (uint32_t)ok << i;
     tok[i] = ok ? (uint32_t)tk : 0u;
   }
-  uint4 vals[16];
+  uint4 vals[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i)
+  for (int i = 0; i < 8; ++i)
     vals[i] = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)tok[i] * a.hq + it.hq) * HEAD_DIM) + ch);
-  if (ok_mask != 0xffffu && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
+  if (ok_mask != 0xffu && a.status) atomicCAS(a.status, 0, (int)DEV_BAD_INDEX);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int r = i * 8 + (row >> 4);
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 16 + (idx >> 4);
     const bool keep = (r < nrows) && ((ok_mask >> i) & 1u);
     uint4 v = vals[i];
     if (!keep) v = make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(sQt + (ch >> 3) * BLK_BYTES + sw128_offset((uint32_t)r, (uint32_t)(ch & 7) * 8)) = v;
   }
   fence_proxy_async_smem();
+}
+
+// A [32 rows][16 columns] bf16 patch (8 packed words per lane, lane == row) goes through a warp-private
+// 1 KB buffer and out with two lanes per row: one store instruction covers 16 rows x 32 contiguous
+// bytes (whole sectors). 16-byte chunks are XOR-swizzled by (row / 4) so neither pass has bank conflicts.
+//   my_row_off : element offset of (this lane's row, first column of the patch), or -1 to skip the row
+__device__ __forceinline__ void store_patch_32x16(uint8_t* stage, const uint32_t* pk, __nv_bfloat16* base,
+                                                  long long my_row_off, int lane) {
+  uint8_t* wr = stage + lane * 32;
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+    *reinterpret_cast<uint4*>(wr + (((c ^ (lane >> 2)) & 1) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int r = 16 * k + (lane >> 1), c = lane & 1;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 32 + (((c ^ (r >> 2)) & 1) << 4));
+    const long long off = __shfl_sync(0xffffffffu, my_row_off, r);
+    if (off >= 0) *reinterpret_cast<uint4*>(base + off + c * 8) = v;
+  }
+  __syncwarp();
 }
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -164,7 +193,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
   __shared__ uint64_t k_full[FWD_STAGES], k_empty[FWD_STAGES], v_full[FWD_STAGES], v_empty[FWD_STAGES];
   __shared__ uint64_t q_ready[2], s_full[2], p_ready[2], o_done[2];
-  __shared__ __align__(16) uint8_t s_stage[8][2048];   // per-warp staging of the epilogue stores
+  __shared__ __align__(16) uint8_t s_stage[FWD_SM_WARPS][1024];   // per-warp staging of the epilogue stores
+  __shared__ float s_xch[2][FWD_SM_WARPS][32];   // row maxima / row sums handed to the row's other thread
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_items[ITEM_RING * ITEM_WORDS];
@@ -185,12 +215,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mbar_init(&v_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&q_ready[t], TILE / 32);   // one arrival per warp
+      mbar_init(&q_ready[t], FWD_SM_WARPS / 2);   // one arrival per warp
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_ready[t], TILE / 32);
+      mbar_init(&p_ready[t], FWD_SM_WARPS / 2);
       mbar_init(&o_done[t], 1);
     }
-    ring_init(ring, 9);   // eight softmax warps + the MMA warp
+    ring_init(ring, FWD_SM_WARPS + 1);   // the softmax warps + the MMA warp
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -205,19 +235,32 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   const int total_pairs = __ldg(a.n_tiles);
   const long long total_items = (long long)total_pairs * a.hq;
 
-  if (warp < 8) {
+  if (warp < FWD_SM_WARPS) {
     // =====================================================================================
     // softmax groups
     // =====================================================================================
-    const int t = warp >> 2;              // query tile of this group
-    const int row = tid & (TILE - 1);     // row inside the tile == TMEM lane
+    const int t = warp >> 3;              // query tile of this group
+    const int h = (warp >> 2) & 1;        // column half: keys / output columns [64 h, 64 h + 64)
+    const int row = (warp & 3) * 32 + lane;   // row inside the tile == TMEM lane (a warp reaches lanes 32 * (warp % 4) ..)
+    const int idx = tid & 255;            // thread index inside the tile's group
+    const int pair_bar = 1 + (warp & 3) + 4 * t;   // named barrier of the two warps that share these rows
+    const int partner = warp ^ 4;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + (uint32_t)t * 128u + lane_off;
-    const uint32_t tO = tmem + 256u + (uint32_t)t * 128u + lane_off;
+    const uint32_t tS = tmem + (uint32_t)t * 128u + lane_off + (uint32_t)h * 64u;   // this half's scores
+    const uint32_t tP = tS;   // this half's probabilities (bf16, 32 columns) overwrite the start of its own scores
+    const uint32_t tO = tmem + 256u + (uint32_t)t * 128u + lane_off + (uint32_t)h * 64u;
     uint8_t* sQt = sQ + t * TILE_BYTES;
     const float c = a.scale_log2;
     uint32_t n_steps = 0;   // (tile, key-step) pairs processed so far == S / P / O barrier phases
-    uint32_t n_items = 0;   // items in which this tile was active
+    uint32_t n_xch = 0;     // exchanges with the row's other thread so far (slot parity)
+
+    // hands `mine` to the row's other thread and returns its value; every thread of both warps calls it
+    auto exchange = [&](float mine) -> float {
+      const uint32_t slot = n_xch++ & 1u;
+      s_xch[slot][warp][lane] = mine;
+      named_barrier_sync(pair_bar, 64);
+      return s_xch[slot][partner][lane];
+    };
 
     // Items are walked one ahead: as soon as the last score tile of an item has been read, the
     // rows of the NEXT item are copied into shared memory (Q is free by then), so the tensor pipe
@@ -227,7 +270,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     long long w = ring_pop(ring, n_ring, it, ab);
     if (w >= 0) {
       if (it.nrows[t] > 0) {
-        gather_query_tile(a, it, t, row, sQt);
+        gather_query_tile(a, it, t, idx, sQt);
         tc_fence_before();
         mbar_arrive_warp(&q_ready[t]);
       }
@@ -240,7 +283,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         w_next = ring_pop(ring, n_ring + 1, it_next, ab);
         if (w_next >= 0) {
           if (it_next.nrows[t] > 0) {
-            gather_query_tile(a, it_next, t, row, sQt);
+            gather_query_tile(a, it_next, t, idx, sQt);
             tc_fence_before();
             mbar_arrive_warp(&q_ready[t]);
           }
@@ -257,7 +300,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const int my_pos = row_position(a, it.bos_q, r_base + my_r);
       const int min_pos = it.min_pos[t], max_pos = it.max_pos[t];
       float m_run = -INFINITY;
-      float l_run = 0.f;
+      float l_run = 0.f;   // this half's share of the row sum
 
       for (int j = it.jb[t]; j < it.je[t]; ++j) {
         const bool first = (j == it.jb[t]);
@@ -268,22 +311,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         mbar_wait(&s_full[t], n_steps & 1u, ab);
         tc_fence_after();
 
-        // ---- the whole score row (128 fp32) comes into registers with one wait ----
-        uint32_t s0[32], s1[32], s2[32], s3[32];
-        tmem_ld32(tS, s0);
-        tmem_ld32(tS + 32, s1);
-        tmem_ld32(tS + 64, s2);
-        tmem_ld32(tS + 96, s3);
-        tmem_ld_wait();
-        if (masked) {
-          mask_chunk(s0, j * TILE, key_hi, key_lo);
-          mask_chunk(s1, j * TILE + 32, key_hi, key_lo);
-          mask_chunk(s2, j * TILE + 64, key_hi, key_lo);
-          mask_chunk(s3, j * TILE + 96, key_hi, key_lo);
+        // ---- this half of the score row (64 fp32): maximum first; the second 32 columns are read again
+        //      for the exponentials instead of being held (96 registers per thread at this block size) ----
+        uint32_t s0[32];
+        float mx_half;
+        {
+          uint32_t s1[32];
+          tmem_ld32(tS, s0);
+          tmem_ld32(tS + 32, s1);
+          tmem_ld_wait();
+          if (masked) {
+            mask_chunk(s0, j * TILE + h * 64, key_hi, key_lo);
+            mask_chunk(s1, j * TILE + h * 64 + 32, key_hi, key_lo);
+          }
+          mx_half = fmaxf(max_chunk(s0), max_chunk(s1));
         }
-        const float mx = fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
+        const float mx = fmaxf(mx_half, exchange(mx_half));   // row maximum over both halves
 
-        // ---- running maximum, lazy rescale of O ----
+        // ---- running maximum, lazy rescale of O (both threads of a row take the same decision) ----
         if (first) {
           m_run = mx;
         } else {
@@ -300,7 +345,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
               l_run *= alpha;
             }
 #pragma unroll 1
-            for (int chk = 0; chk < 4; ++chk) {
+            for (int chk = 0; chk < 2; ++chk) {
               uint32_t r[32];
               tmem_ld32(tO + chk * 32, r);
               tmem_ld_wait();
@@ -318,13 +363,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         {
           uint32_t pk[16];
           exp_pack_chunk(s0, c, mc, pk, l0, l1);
-          tmem_st16(tS, pk);
-          exp_pack_chunk(s1, c, mc, pk, l0, l1);
-          tmem_st16(tS + 16, pk);
-          exp_pack_chunk(s2, c, mc, pk, l0, l1);
-          tmem_st16(tS + 32, pk);
-          exp_pack_chunk(s3, c, mc, pk, l0, l1);
-          tmem_st16(tS + 48, pk);
+          tmem_ld32(tS + 32, s0);   // columns 32-63 again (the store below only touches columns 0-15)
+          tmem_ld_wait();
+          tmem_st16(tP, pk);
+          if (masked) mask_chunk(s0, j * TILE + h * 64 + 32, key_hi, key_lo);
+          exp_pack_chunk(s0, c, mc, pk, l0, l1);
+          tmem_st16(tP + 16, pk);
         }
         l_run += l0 + l1;
         tmem_st_wait();
@@ -337,14 +381,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const bool row_valid = row < nrows;
       const long long tok = row_valid ? row_token(a, it.bos_q, it.bos_k, r_base + row) : -1;
       const bool store = row_valid && tok >= 0 && tok < a.n_tokens;
-      const float inv_l = 1.f / l_run;
-      __nv_bfloat16* orow = a.o + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM;
-      float* lse_out = (store && a.lse) ? a.lse + (size_t)tok * a.hq + it.hq : nullptr;
+      const float l_row = l_run + exchange(l_run);
+      const float inv_l = 1.f / l_row;
+      __nv_bfloat16* orow = a.o + ((size_t)(store ? tok : 0) * a.hq + it.hq) * HEAD_DIM + h * 64;
+      float* lse_out = (store && a.lse && h == 0) ? a.lse + (size_t)tok * a.hq + it.hq : nullptr;
 
       w_next = ring_pop(ring, n_ring + 1, it_next, ab);
       if (w_next >= 0) {
         if (it_next.nrows[t] > 0) {
-          gather_query_tile(a, it_next, t, row, sQt);
+          gather_query_tile(a, it_next, t, idx, sQt);
           tc_fence_before();
           mbar_arrive_warp(&q_ready[t]);
         }
@@ -354,23 +399,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       tc_fence_after();
       const long long row_off = store ? (long long)(orow - a.o) : -1;
 #pragma unroll 1
-      for (int chk = 0; chk < 4; ++chk) {
+      for (int chk = 0; chk < 2; ++chk) {
         uint32_t r[32], pk[16];
         tmem_ld32(tO + chk * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-        store_patch_32x32(s_stage[warp], pk, a.o, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+        store_patch_32x16(s_stage[warp], pk, a.o, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+        store_patch_32x16(s_stage[warp], pk + 8, a.o, row_off >= 0 ? row_off + chk * 32 + 16 : -1, lane);
       }
-      if (lse_out) *lse_out = m_run * c + log2f(l_run);
+      if (lse_out) *lse_out = m_run * c + log2f(l_row);
       tc_fence_before();
       ring_release(ring, n_ring);
       it = it_next;
       w = w_next;
       ++n_ring;
     }
-  } else if (warp == 8) {
+  } else if (warp == FWD_SM_WARPS) {
     // =====================================================================================
     // TMA producer
     // =====================================================================================
@@ -438,7 +484,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, uint32_t st, bool acc) {
-        umma_tile_k128<true, true>(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u,
+        umma_tile_k128<true, true, 2>(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u,
                                    umma_desc_sw128(v_base + st * TILE_BYTES, BLK_BYTES, 1024), idesc_pv, acc ? 1u : 0u);
         umma_commit(&o_done[t]);
       };

@@ -387,6 +387,11 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
+// barrier among `nthreads` threads (a multiple of 32) that name the same id (1..15; 0 is __syncthreads)
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // max of three floats in one instruction (3-input max.f32, sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
