@@ -12,6 +12,10 @@ Metric: TFLOP/s on the EFFECTIVE FLOPs of the selected rows,
 ``F_fwd = 4 * 128 * HQ * sum_{selected rows}(pos + 1)``, ``F_step = 3.5 * F_fwd``.
 Masked / padded tile work and the recomputation of S in the backward are not counted.
 
+The K timed steps carry one CUDA event per step and nothing else; the per-kernel durations behind
+``roofline`` and ``kernel_ms`` come from a second pass of the same K steps with an event pair
+around every kernel (those pairs cost several per cent of the step, see ``kernel_ms_pass``).
+
 With N > 1 (one process per GPU under torchrun) every rank runs its own batch (weak
 scaling, no collective on the data path); the value is the sum of FLOPs over ranks divided
 by the slowest rank's device time.
@@ -210,13 +214,12 @@ def run_gpu(args):
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     for ev in [e0, e1] + marks:
         ev.record()
-    _lib.check(lib.logo_profile_reserve(8 * (args.steps + args.warmup)), "logo_profile_reserve")
-    lib.logo_profile_enable(1)
+    _lib.check(lib.logo_profile_reserve(8 * (args.steps + 2)), "logo_profile_reserve")
+    lib.logo_profile_enable(0)
     for _ in range(args.warmup):
         m, *_ = device_step(batch)
     torch.cuda.synchronize()
     ops.check_device_status(m.status, "warm-up")
-    lib.logo_profile_read(None, None, 7)      # drop the warm-up launches (their events go back to the pool)
     barrier()
     sampler.begin()
     e0.record()
@@ -225,19 +228,35 @@ def run_gpu(args):
         marks[i].record()
     e1.record()
     barrier()
-    lib.logo_profile_enable(0)
     per_step = [a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks)]
     clocks = sampler.finish()
     ms_total = e0.elapsed_time(e1)
     ops.check_device_status(m.status, "timed region")
+
+    # ---- per-kernel durations: the same K steps once more, with a CUDA event pair around every kernel.
+    # The pairs cost several per cent of the step (a dozen extra stream operations between kernels that
+    # are 20 us to 1.4 ms long), so they stay out of the pass that gives `value`.
     import ctypes
+    lib.logo_profile_enable(1)
+    for _ in range(2):
+        device_step(batch)
+    torch.cuda.synchronize()
+    lib.logo_profile_read(None, None, 7)      # drop those two steps (their events go back to the pool)
+    ek0, ek1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ek0.record()
+    for i in range(args.steps):
+        device_step(batch)
+    ek1.record()
+    torch.cuda.synchronize()
+    lib.logo_profile_enable(0)
+    ms_step_with_events = ek0.elapsed_time(ek1) / args.steps
     kinds = ["select", "attn_fwd", "bwd_preprocess", "bwd_dkv", "bwd_dq", "bwd_fused", "bwd_finish"]
     tot = (ctypes.c_double * len(kinds))()
     cnt = (ctypes.c_int * len(kinds))()
     lib.logo_profile_read(ctypes.cast(tot, ctypes.c_void_p), ctypes.cast(cnt, ctypes.c_void_p), len(kinds))
     kernel_ms = {name: (tot[i] / cnt[i] if cnt[i] else None) for i, name in enumerate(kinds)}
     # select = 2 kernels per call; forward and backward each launch one zero_unselected_rows_kernel
-    # (counted with the forward and with the preprocess kernel)
+    # (counted with the forward and with the preprocess kernel); the count is that of K steps
     launches = 2 * cnt[0] + 2 * cnt[1] + 2 * cnt[2] + cnt[3] + cnt[4] + cnt[5] + cnt[6]
 
     # ---- e2e: public API, host buffers, copies inside the timed region ----
@@ -391,6 +410,8 @@ def run_gpu(args):
         "clocks": clocks,
         "roofline": roofline,
         "kernel_ms": kernel_ms, "kernel_tflops": kernel_tflops,
+        "kernel_ms_pass": {"what": "the same K steps repeated with a CUDA event pair around every kernel",
+                           "ms_per_step_with_events": ms_step_with_events},
         "frac_of_peak_fwd_bwd": value / world / peaks["bf16"],
         # the step slows by ~10 % over its first ~25 repetitions as the power controller settles
         # (2.38 -> 2.65 ms): short runs compare with the burst peak, long ones with the sustained one
