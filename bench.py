@@ -12,7 +12,8 @@ Metric: TFLOP/s on the EFFECTIVE FLOPs of the selected rows,
 ``F_fwd = 4 * 128 * HQ * sum_{selected rows}(pos + 1)``, ``F_step = 3.5 * F_fwd``.
 Masked / padded tile work and the recomputation of S in the backward are not counted.
 
-The K timed steps carry one CUDA event per step and nothing else; the per-kernel durations behind
+The K timed steps are replays of one CUDA graph (the step's three C-ABI calls captured once) and
+carry one CUDA event per step and nothing else; the per-kernel durations behind
 ``roofline`` and ``kernel_ms`` come from a second pass of the same K steps with an event pair
 around every kernel (those pairs cost several per cent of the step, see ``kernel_ms_pass``).
 
@@ -216,15 +217,35 @@ def run_gpu(args):
         ev.record()
     _lib.check(lib.logo_profile_reserve(8 * (args.steps + 2)), "logo_profile_reserve")
     lib.logo_profile_enable(0)
-    for _ in range(args.warmup):
+    # One step = three C-ABI calls = nine launches, the shortest 10 us long. They are captured once and
+    # replayed as one CUDA graph per step: launched one by one from Python, the first step after the
+    # barrier waits on the host for every launch (0.3 ms alone, several ms with 8 ranks and their NCCL
+    # threads on the same cores), which a 20-step measurement shows as 1-8 % of the total.
+    launch = "one CUDA graph per step (select + forward + backward captured once)"
+    try:
+        for _ in range(2):
+            m, *_ = device_step(batch)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            m, *_ = device_step(batch)
+        run_step = graph.replay
+    except Exception as exc:   # noqa: BLE001 - any capture problem means: measure the plain launches
+        print(f"step not captured ({type(exc).__name__}: {exc}); timing plain launches", file=sys.stderr)
+        launch = "plain launches"
         m, *_ = device_step(batch)
+
+        def run_step():
+            device_step(batch)
+    for _ in range(args.warmup):
+        run_step()
     torch.cuda.synchronize()
     ops.check_device_status(m.status, "warm-up")
     barrier()
     sampler.begin()
     e0.record()
     for i in range(args.steps):
-        m, *_ = device_step(batch)
+        run_step()
         marks[i].record()
     e1.record()
     barrier()
@@ -403,7 +424,7 @@ def run_gpu(args):
         "config": {"workload": "sq_full_attn fwd+bwd, 4x8192 tokens packed [1,32768,16,128], causal, "
                                f"Bernoulli({args.ratio}) row mask", "ratio": args.ratio,
                    "l2": "inputs (671 MB per step) exceed the 126 MB L2; no flush needed",
-                   "effective_flops_per_step": f_step},
+                   "effective_flops_per_step": f_step, "launch": launch},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
