@@ -856,12 +856,12 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   LOGO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, LOGO_ERR_INVALID,
                "attention backward workspace must be 256-byte aligned");
 
-  if (gathered) {   // dQ of unselected rows is zero; the selected rows are written by the dQ kernel
+  const bool fused = g_bwd_mode[gathered ? 0 : 1].load(std::memory_order_relaxed) == 0;
+  if (gathered && !fused) {   // dQ of unselected rows is zero (the single-pass kernel writes the zeros itself)
     const int rc0 = launch_zero_unselected_rows(dq, q_idx, sq_ptr, n_tokens,
                                                 (size_t)hq * HEAD_DIM * sizeof(__nv_bfloat16), stream);
     if (rc0) return rc0;
   }
-  const bool fused = g_bwd_mode[gathered ? 0 : 1].load(std::memory_order_relaxed) == 0;
 
   const int sms = sm_count();
   prof_begin(PROF_BWD_PRE, stream);
@@ -884,6 +884,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
 
   BwdArgs a{};
   a.q_idx = q_idx;
+  a.sq_ptr = sq_ptr;
   a.pos_ids = pos_ids;
   a.cu_q = cu_q;
   a.cu_k = cu_k;

@@ -10,6 +10,7 @@ namespace logo {
 
 struct BwdArgs {
   const int64_t* q_idx;       // null: identity (local branch)
+  const int32_t* sq_ptr;      // [1] number of selected rows (with q_idx)
   const int32_t* pos_ids;
   const int32_t* cu_q;
   const int32_t* cu_k;

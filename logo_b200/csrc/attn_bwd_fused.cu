@@ -23,7 +23,8 @@
 //
 // Warp roles (512 threads = four warpgroups): 0-7 element-wise (lane quarter w % 4, 64 query
 // columns each), 8-11 dQ read-out (one per lane quarter), 12 TMA producer + work claiming, 13 MMA
-// issue, 14-15 idle. The kernel starts with 128 registers per thread; the element-wise warpgroups
+// issue, 14-15 zero the dQ rows of the tokens the selection leaves out (HBM traffic that hides under
+// the products). The kernel starts with 128 registers per thread; the element-wise warpgroups
 // raise their share to 160 with setmaxnreg (they keep a 64-column fp32 P row and a dP chunk live),
 // the read-out warpgroup takes 144 (a whole 128-column row of dQ^T in registers, so that Y is released
 // after one round of loads) and the last one drops to 48: every scheduler holds one warp of each
@@ -436,6 +437,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         while (globaltimer_ns() - t0 < 2000000ull) {
         }
       }
+    }
+   } else if (warp > FUSED_EW_WARPS + FUSED_DQ_WARPS + 1) {
+    // ================= the two spare warps: dQ of the rows the selection leaves out is zero =================
+    if (a.q_idx) {
+      const int sq = min(max(__ldg(a.sq_ptr), 0), a.n_tokens);
+      zero_unselected_rows_part(reinterpret_cast<uint4*>(a.dq), a.q_idx, sq, a.n_tokens, a.hq * HEAD_DIM / 8,
+                                blockIdx.x * 2 + (warp - (FUSED_EW_WARPS + FUSED_DQ_WARPS + 2)), gridDim.x * 2, lane);
     }
    } else if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS + 1) {
     // ================= MMA issuer: the whole warp walks this code, an elected lane issues =================

@@ -177,38 +177,12 @@ extern "C" int logo_last_error(char* buf, int n) {
 // ---------------------------------------------------------------------------------------
 namespace logo {
 
-// One warp per run of 32 consecutive tokens: a binary search finds the first selected token at or
-// after the run's start, the next 32 entries of q_idx (one per lane) mark which tokens of the run are
-// selected, and the warp zeroes the rows of the others. Work is balanced whatever the selection
-// looks like (an empty selection zeroes everything with all warps).
 __global__ void __launch_bounds__(256)
     zero_unselected_rows_kernel(uint4* __restrict__ base, const int64_t* __restrict__ q_idx,
                                 const int32_t* __restrict__ sq_ptr, int n_tokens, int row_chunks) {
   const int sq = min(max(__ldg(sq_ptr), 0), n_tokens);
-  const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * blockDim.x) >> 5;
-  const int n_runs = (n_tokens + 31) >> 5;
-  for (int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; run < n_runs; run += warps) {
-    const long long t0 = (long long)run * 32;
-    int lo = 0, hi = sq;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (__ldg(q_idx + mid) < t0) lo = mid + 1; else hi = mid;
-    }
-    unsigned bit = 0;
-    if (lo + lane < sq) {
-      const long long off = __ldg(q_idx + lo + lane) - t0;   // >= 0 by the search
-      if (off >= 0 && off < 32) bit = 1u << (int)off;
-    }
-    const unsigned selected = __reduce_or_sync(0xffffffffu, bit);
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-      const long long tok = t0 + i;
-      if (tok >= n_tokens || ((selected >> i) & 1u)) continue;
-      uint4* row = base + (size_t)tok * row_chunks;
-      for (int c = lane; c < row_chunks; c += 32) row[c] = make_uint4(0, 0, 0, 0);
-    }
-  }
+  zero_unselected_rows_part(base, q_idx, sq, n_tokens, row_chunks, (blockIdx.x * blockDim.x + threadIdx.x) >> 5,
+                            (gridDim.x * blockDim.x) >> 5, threadIdx.x & 31);
 }
 
 int launch_zero_unselected_rows(void* base, const int64_t* q_idx, const int32_t* sq_ptr, int n_tokens,

@@ -48,6 +48,40 @@ int sm_count();
 int launch_zero_unselected_rows(void* base, const int64_t* q_idx, const int32_t* sq_ptr, int n_tokens,
                                 size_t row_bytes, cudaStream_t stream);
 
+#ifdef __CUDACC__
+// The device side of it, for one warp that is number `part` of `n_parts` warps sharing the job: each
+// warp takes runs of 32 consecutive tokens; a binary search finds the first selected token at or after
+// the run's start, the next 32 entries of q_idx (one per lane) mark which tokens of the run are
+// selected, and the warp zeroes the rows (row_chunks 16-byte pieces each) of the others. Work is
+// balanced whatever the selection looks like (an empty selection zeroes everything with all warps).
+__device__ __forceinline__ void zero_unselected_rows_part(uint4* __restrict__ base, const int64_t* __restrict__ q_idx,
+                                                          int sq, int n_tokens, int row_chunks, int part, int n_parts,
+                                                          int lane) {
+  const int n_runs = (n_tokens + 31) >> 5;
+  for (int run = part; run < n_runs; run += n_parts) {
+    const long long t0 = (long long)run * 32;
+    int lo = 0, hi = sq;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(q_idx + mid) < t0) lo = mid + 1; else hi = mid;
+    }
+    unsigned bit = 0;
+    if (lo + lane < sq) {
+      const long long off = __ldg(q_idx + lo + lane) - t0;   // >= 0 by the search
+      if (off >= 0 && off < 32) bit = 1u << (int)off;
+    }
+    const unsigned selected = __reduce_or_sync(0xffffffffu, bit);
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      const long long tok = t0 + i;
+      if (tok >= n_tokens || ((selected >> i) & 1u)) continue;
+      uint4* row = base + (size_t)tok * row_chunks;
+      for (int c = lane; c < row_chunks; c += 32) row[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+#endif
+
 // Per-kernel event timing (see logo_profile_enable): kernels report under these indices.
 enum ProfKind {
   PROF_SELECT = 0, PROF_ATTN_FWD = 1, PROF_BWD_PRE = 2, PROF_BWD_DKV = 3, PROF_BWD_DQ = 4, PROF_BWD_FUSED = 5,
