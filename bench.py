@@ -276,10 +276,10 @@ def run_gpu(args):
     cnt = (ctypes.c_int * len(kinds))()
     lib.logo_profile_read(ctypes.cast(tot, ctypes.c_void_p), ctypes.cast(cnt, ctypes.c_void_p), len(kinds))
     kernel_ms = {name: (tot[i] / cnt[i] if cnt[i] else None) for i, name in enumerate(kinds)}
-    # select = 2 kernels per call; the forward launches one zero_unselected_rows_kernel (counted with it), the
-    # two-kernel backward another (counted with the preprocess kernel; the single-pass kernel writes those
-    # zeros itself); the count is that of K steps
-    launches = 2 * cnt[0] + 2 * cnt[1] + cnt[2] + (cnt[2] if cnt[5] == 0 else 0) + cnt[3] + cnt[4] + cnt[5] + cnt[6]
+    # select = 2 kernels per call; the two-kernel backward launches one zero_unselected_rows_kernel (counted
+    # with the preprocess kernel; the forward and the single-pass backward write those zeros themselves);
+    # the count is that of K steps
+    launches = 2 * cnt[0] + cnt[1] + cnt[2] + (cnt[2] if cnt[5] == 0 else 0) + cnt[3] + cnt[4] + cnt[5] + cnt[6]
 
     # ---- e2e: public API, host buffers, copies inside the timed region ----
     # Every step copies ITS inputs from pinned host memory and reads ITS results back to pinned host

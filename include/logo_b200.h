@@ -144,7 +144,7 @@ int logo_select_rows_static(const void* gate, int gate_dtype, const void* thres,
  *   q [n_tokens, hq, 128], k, v [n_tokens, h, 128] bf16, contiguous; hq % h == 0
  *   q_idx, pos_ids, cu_seqlens_q, tile_off, meta: outputs of logo_select_rows
  *   o   [n_tokens, hq, 128] bf16: rows listed in q_idx are written; with zero_fill != 0 every other
- *       row is set to 0 first (the reference returns zeros for unselected rows, :469-471)
+ *       row is set to 0 by the same kernel (the reference returns zeros for unselected rows, :469-471)
  *   lse [n_tokens, hq] fp32 or NULL: base-2 log-sum-exp of scale * log2(e) * q.k for selected rows
  *       (the reference keeps it compacted, :118-121; here it is indexed by token)
  *   scale: softmax scale, > 0 (the reference default is 128 ** -0.5, :523-524)

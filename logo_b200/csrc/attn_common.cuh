@@ -42,6 +42,8 @@ struct AttnArgs {
   int window;                // 0: full causal; w > 0: keys [pos - w, pos]
   float scale_log2;          // softmax scale * log2(e)
   float scale;               // softmax scale
+  const int32_t* zero_sq;    // forward: when set ([1] number of selected rows), two spare warps of every CTA zero
+                             // the rows of `o` that the selection leaves out
   int* status;
 };
 

@@ -6,12 +6,13 @@
 //
 // A work item is a pair of query tiles (2 x 128 compacted rows of one sequence and one head);
 // the kernel is persistent (one CTA per SM claims items from a global counter through the record
-// ring of attn_common.cuh). Eighteen warps:
+// ring of attn_common.cuh). Twenty warps:
 //   warps 0-7 / 8-15 : softmax groups for query tile 0 / 1, two threads per row: warps 0-3 (8-11) take
 //                      keys 0-63 of the score tile and output columns 0-63, warps 4-7 (12-15) the other
 //                      half; the two threads of a row exchange their maxima through shared memory
 //   warp 16          : claims / decodes items, TMA producer of the 128-key K and V tiles (2-stage rings)
 //   warp 17          : issues tcgen05.mma (whole warp walks the loop, an elected lane issues)
+//   warps 18-19      : global branch: zero the output rows of the tokens the selection leaves out
 // A tile's softmax sits on the chain scores -> softmax -> P*V -> next scores (P overwrites S); with one
 // thread per row that step took about 2500 clocks against 1024 clocks of tensor-pipe work per tile, so
 // the tiles' softmax phases overlapped and shared the special-function unit. Halving the row work per
@@ -32,7 +33,7 @@
 namespace logo {
 
 constexpr int FWD_SM_WARPS = 16;   // softmax warps: 2 tiles x 2 column halves x 4 row quarters
-constexpr int FWD_THREADS = (FWD_SM_WARPS + 2) * 32;
+constexpr int FWD_THREADS = (FWD_SM_WARPS + 4) * 32;   // + producer, MMA issuer, two spare warps
 constexpr int FWD_STAGES = 2;
 constexpr int FWD_SMEM_BYTES = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -466,6 +467,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
       }
     }
+  } else if (warp > FWD_SM_WARPS + 1) {
+    // =====================================================================================
+    // spare warps: the output rows of unselected tokens are zero (HBM traffic that hides under the products)
+    // =====================================================================================
+    if (a.zero_sq && a.q_idx) {
+      const int sq = min(max(__ldg(a.zero_sq), 0), a.n_tokens);
+      zero_unselected_rows_part(reinterpret_cast<uint4*>(a.o), a.q_idx, sq, a.n_tokens, a.hq * HEAD_DIM / 8,
+                                blockIdx.x * 2 + (warp - (FWD_SM_WARPS + 2)), gridDim.x * 2, lane);
+    }
   } else {
     // =====================================================================================
     // MMA issuer: the whole warp walks this code, an elected lane issues (see umma_ss)
@@ -596,10 +606,6 @@ extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, voi
   if (n_tokens == 0 || n_seq == 0) return LOGO_OK;
   LOGO_REQUIRE(q_idx && pos_ids && cu_seqlens_q && cu_seqlens_k && tile_off && meta, LOGO_ERR_INVALID,
                "selection metadata pointers must not be NULL");
-  if (zero_fill) {   // only the rows the kernel will not write
-    rc = launch_zero_unselected_rows(o, q_idx, meta, n_tokens, (size_t)hq * HEAD_DIM * sizeof(__nv_bfloat16), stream);
-    if (rc) return rc;
-  }
   AttnArgs a{};
   a.q = (const __nv_bfloat16*)q;
   a.k = (const __nv_bfloat16*)k;
@@ -618,6 +624,7 @@ extern "C" int logo_sq_attn_fwd(const void* q, const void* k, const void* v, voi
   a.hq = hq;
   a.h = h;
   a.window = 0;
+  a.zero_sq = zero_fill ? meta : nullptr;   // meta[0] = number of selected rows
   a.scale = scale;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
