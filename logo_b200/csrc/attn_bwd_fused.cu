@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FusedSmem::BARS);
   uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
            *do_empty = bars + 8, &st_full = bars[10], &dpt_full = bars[11], &p_ready = bars[12], &ds_ready = bars[13],
-           &dq_full = bars[14], &dv_done = bars[15], &dq_read = bars[16], &x_free = bars[17], &acc_done = bars[18];
+           &dq_full = bars[14], &dv_done = bars[15], &dq_read = bars[16], &acc_read = bars[17], &acc_done = bars[18];
   const ItemRing ring{reinterpret_cast<int*>(smem + FusedSmem::ITEMS), bars + 19, bars + 19 + ITEM_RING};
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + FusedSmem::MISC);
   int& abort_flag = *reinterpret_cast<int*>(smem + FusedSmem::MISC + 4);
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     mbar_init(&dq_full, 1);
     mbar_init(&dv_done, 1);
     mbar_init(&dq_read, FUSED_DQ_WARPS);
-    mbar_init(&x_free, 1);
+    mbar_init(&acc_read, FUSED_DQ_WARPS);   // one arrival per read-out warp
     mbar_init(&acc_done, 1);
     ring_init(ring, FUSED_EW_WARPS + FUSED_DQ_WARPS + 1);
     fence_barrier_init();
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const int col0 = half * 64;
     const float c = a.scale_log2;
-    uint32_t idx = 0, n_items = 0;
+    uint32_t idx = 0;
 
     // lse / delta / pos of row `tid` of query tile `i` of head `hq`: loaded unconditionally from a
     // clamped row into registers (threads 0-127), stored to the shared vectors between two steps
@@ -274,31 +274,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         named_barrier_sync(3, 256);
       }
 
-      // ---- epilogue: dK * scale, dV -> bf16 rows (staged through X, free once the last dQ tile has left) ----
-      mbar_wait(&acc_done, n_items & 1u, ab);
-      mbar_wait(&x_free, n_items & 1u, ab);
-      tc_fence_after();
-      ++n_items;
-      {
-        const long long row_off =
-            key_valid ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM + col0) : -1;
-        uint8_t* stage = sX + warp * 2048;
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off + (uint32_t)col0;
-          const float mul = (which == 0) ? a.scale : 1.f;
-#pragma unroll
-          for (int chk = 0; chk < 2; ++chk) {
-            uint32_t r[32], pk[16];
-            tmem_ld32(base + chk * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
-            store_patch_32x32(stage, pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
-          }
-        }
-      }
+      // (dK and dV of the item are written out by the read-out warps)
       tc_fence_before();
       ring_release(ring, n_ring);
       it = it_next;
@@ -317,7 +293,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const bool issuer = (warp == FUSED_EW_WARPS) && (lane == 0);
     float* stage = reinterpret_cast<float*>(sX) + quad * 32 + lane;
-    uint32_t idx = 0;
+    uint32_t idx = 0, n_items = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
       const long long w = ring_pop(ring, n_ring, it, ab);
@@ -371,9 +347,39 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           }
         }
       }
-      // one phase per ITEM (a waiter must see every phase of a barrier, and the element-wise warps only
-      // look at this one at the end of an item): X may take the item's output staging
-      if (issuer) mbar_arrive(&x_free);
+      // ---- the item's dK * scale and dV -> bf16 rows, staged through X (every reduction of the item
+      //      has read its half of X: the barriers above). The element-wise warps are already at the next
+      //      item; the MMA warp starts its accumulators over once all four warps have read these. ----
+      mbar_wait(&acc_done, n_items & 1u, ab);
+      tc_fence_after();
+      ++n_items;
+      {
+        const int key_pos = it.kv_start + quad * 32 + lane;
+        const long long row_off =
+            key_pos < it.len_k ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM) : -1;
+        uint8_t* out_stage = sX + quad * 2048;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off;
+          const float mul = (which == 0) ? a.scale : 1.f;
+#pragma unroll 1
+          for (int chk = 0; chk < 4; ++chk) {
+            uint32_t r[32], pk[16];
+            tmem_ld32(base + chk * 32, r);
+            tmem_ld_wait();
+            if (which == 1 && chk == 3) {   // the accumulators are in registers / on their way out
+              tc_fence_before();
+              mbar_arrive_warp(&acc_read);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * mul, __uint_as_float(r[2 * i + 1]) * mul);
+            store_patch_32x32(out_stage, pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
+          }
+        }
+        // the next item's first dQ tile is staged in X by all four warps
+        named_barrier_sync(4, FUSED_DQ_WARPS * 32);
+      }
       ring_release(ring, n_ring);
     }
     if (issuer) bulk_wait_all();
@@ -500,6 +506,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         const uint32_t nx = q_iter + 1u, st_n = nx & 1u, ph_n = (nx >> 1) & 1u;
         const bool has_next = (s + 1 < n_steps);
         mbar_wait(&p_ready, q_iter & 1u, ab);
+        // dV / dK start over (accumulate = 0): the previous item's must have been read out
+        if (s == 0 && n_items > 1) mbar_wait(&acc_read, n_items & 1u, ab);
         tc_fence_after();
         issue_dv(do_base + st * TILE_BYTES, s > 0);
         umma_commit(&dv_done);       // the dO tile of this stage may now be overwritten with dS^T
