@@ -13,10 +13,11 @@
 //     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
 //     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
 // dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
-// dedicated warps, laid down as an fp32 [query][head dim] tile in a 32 KB staging tile X, 64 query
-// rows at a time, and added to an fp32 accumulator in global memory by bulk tensor
-// reductions (cp.reduce.async.bulk: the reduction runs in L2 on whole lines; per-thread
-// red.global.add was measured 2.5x slower, bound by the SM's atomic issue rate).
+// dedicated warps; each lays its 32 head-dimension columns down as fp32 [query][32] pieces, 32 query
+// rows at a time, in its own double-buffered part of the 32 KB staging tile X and adds them to an
+// fp32 accumulator in global memory by bulk tensor reductions of its own (cp.reduce.async.bulk: the
+// reduction runs in L2; per-thread red.global.add was measured 2.5x slower, bound by the SM's
+// atomic issue rate; waiting for each reduction before staging the next piece cost 3000 clocks a step).
 // bwd_dq_finish_kernel scales, converts and scatters the accumulator to the token rows afterwards.
 // Tensor memory is full (X, Y, dK, dV = 512 columns): dQ^T shares Y with dP^T, so the next
 // dP^T waits until the read-out warps hold the previous dQ^T in registers.
@@ -286,14 +287,17 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
     // and the 128 query rows of the step as columns. The whole row comes into registers in one round
-    // (Y is released right after it); then the tile goes through X transposed, as fp32
-    // [query row][128], 64 query rows at a time, and a bulk reduction adds each half to dq_acc.
+    // (Y is released right after it). Every warp then works alone: it owns 8 KB of X as two 4 KB
+    // buffers, writes 32 query rows x its 32 head-dimension columns into one as fp32 [query row][32],
+    // and its lane 0 sends the buffer to dq_acc with a bulk reduction of its own. A buffer is reused
+    // only when the reduction issued two rounds earlier has read it, so the reductions (which drain at
+    // about 20 bytes per clock per SM) run under the staging of the following rounds and under the
+    // next step instead of being waited for one by one.
     reg_dec_dq();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const bool issuer = (warp == FUSED_EW_WARPS) && (lane == 0);
-    float* stage = reinterpret_cast<float*>(sX) + quad * 32 + lane;
-    uint32_t idx = 0, n_items = 0;
+    float* const my_x = reinterpret_cast<float*>(sX + quad * 8192);   // this warp's two [32][32] fp32 buffers
+    uint32_t idx = 0, n_items = 0, n_rounds = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
       const long long w = ring_pop(ring, n_ring, it, ab);
@@ -305,7 +309,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       }
       for (int g = 0; g < G; ++g) {
         for (int i = it.i0; i < it.i_end; ++i, ++idx) {
-          const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
+          const int x = (it.kvh * G + g) * HEAD_DIM + quad * 32, y = it.bos_q + i * TILE;
           const int nvalid = min(it.nsel - i * TILE, TILE);
           const bool ok = mbar_wait(&dq_full, idx & 1u, ab);
           tc_fence_after();
@@ -317,47 +321,41 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage[j * HEAD_DIM] = __uint_as_float(r0[j]);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage[(32 + j) * HEAD_DIM] = __uint_as_float(r1[j]);
-          fence_proxy_async_smem();
-          named_barrier_sync(4, FUSED_DQ_WARPS * 32);
           // rows past the last valid query row of the tile hold exact zeros (their dS^T columns are
           // zero); rows past the end of the accumulator are clipped by the tensor map
-          if (issuer && ok) {
-            tma_reduce_add_2d(&tm_dq, sX, x, y);
-            bulk_commit_group();
-            bulk_wait_read_all();
-          }
-          named_barrier_sync(4, FUSED_DQ_WARPS * 32);   // the first half has been read out of X
-          if (nvalid > 64) {
+          auto send = [&](const uint32_t (&r)[32], int k) {
+            float* buf = my_x + (n_rounds & 1u) * 1024;
+            if (lane == 0) bulk_wait_read_but_one();   // the reduction of two rounds ago has read this buffer
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) stage[j * HEAD_DIM] = __uint_as_float(r2[j]);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) stage[(32 + j) * HEAD_DIM] = __uint_as_float(r3[j]);
+            for (int j = 0; j < 32; ++j) buf[j * 32 + lane] = __uint_as_float(r[j]);
             fence_proxy_async_smem();
-            named_barrier_sync(4, FUSED_DQ_WARPS * 32);
-            if (issuer && ok) {
-              tma_reduce_add_2d(&tm_dq, sX, x, y + 64);
+            __syncwarp();
+            if (lane == 0 && ok) {
+              tma_reduce_add_2d(&tm_dq, buf, x, y + 32 * k);
               bulk_commit_group();
-              bulk_wait_read_all();
             }
-            named_barrier_sync(4, FUSED_DQ_WARPS * 32);   // the second half has been read out of X
-          }
+            ++n_rounds;
+          };
+          send(r0, 0);
+          if (nvalid > 32) send(r1, 1);
+          if (nvalid > 64) send(r2, 2);
+          if (nvalid > 96) send(r3, 3);
         }
       }
-      // ---- the item's dK * scale and dV -> bf16 rows, staged through X (every reduction of the item
-      //      has read its half of X: the barriers above). The element-wise warps are already at the next
-      //      item; the MMA warp starts its accumulators over once all four warps have read these. ----
+      // ---- the item's dK * scale and dV -> bf16 rows, staged through this warp's part of X. The
+      //      element-wise warps are already at the next item; the MMA warp starts its accumulators over
+      //      once all four warps have read these. ----
       mbar_wait(&acc_done, n_items & 1u, ab);
       tc_fence_after();
       ++n_items;
+      if (lane == 0) bulk_wait_read_all();   // no reduction still reads this warp's buffers
+      __syncwarp();
       {
         const int key_pos = it.kv_start + quad * 32 + lane;
         const long long row_off =
             key_pos < it.len_k ? (long long)(((size_t)(it.bos_k + key_pos) * a.h + it.kvh) * HEAD_DIM) : -1;
-        uint8_t* out_stage = sX + quad * 2048;
+        uint8_t* out_stage = reinterpret_cast<uint8_t*>(my_x);
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           const uint32_t base = (which == 0 ? TM_DK : TM_DV) + lane_off;
@@ -377,12 +375,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
             store_patch_32x32(out_stage, pk, which == 0 ? a.dk : a.dv, row_off >= 0 ? row_off + chk * 32 : -1, lane);
           }
         }
-        // the next item's first dQ tile is staged in X by all four warps
-        named_barrier_sync(4, FUSED_DQ_WARPS * 32);
       }
       ring_release(ring, n_ring);
     }
-    if (issuer) bulk_wait_all();
+    if (lane == 0) bulk_wait_all();   // the reductions of this warp are performed before the CTA leaves
   } else {
    reg_dec_misc();
    if (warp == FUSED_EW_WARPS + FUSED_DQ_WARPS) {
@@ -585,8 +581,9 @@ int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, con
   prof_begin(PROF_BWD_FUSED, stream);
   CUtensorMap tm_dq;
   const uint64_t acc_rows = a.q_idx ? (uint64_t)a.cap : (uint64_t)a.n_tokens;
+  // one reduction = 32 query rows x 32 head-dimension columns (a 128-byte piece of each row)
   const int rc = make_tmap_2d_f32(&tm_dq, dq_acc, (uint64_t)a.hq * HEAD_DIM, acc_rows, (uint64_t)a.hq * HEAD_DIM * 4,
-                                  HEAD_DIM, 64);
+                                  32, 32);
   if (rc) return rc;
   attn_bwd_fused_kernel<<<sms, FUSED_THREADS, FusedSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, a);
   prof_end(PROF_BWD_FUSED, stream);
