@@ -363,6 +363,8 @@ int logo_profile_read(double* total_ms, int* launches, int n);
  *   mode 1: C = A * B     (B row-major [k][n], i.e. MN-major operand)
  *   mode 2: C = A * B     (A staged in tensor memory, B MN-major)
  *   mode 3: C = A^T * B   (both operands MN-major: rows of a and b are the reduction index)
+ *   mode 4: C = A * B^T + A[:, 0:16] * B[:, 0:16]^T   (mode 0 plus a ninth k-step whose [128][16]
+ *           operand tiles use the 32-byte swizzle)
  *   a, b: bf16 [128][128] row-major; c: fp32 [128][128]
  *   flags bit 0 / bit 2: stage A / B through thread-written swizzled shared memory instead of TMA.
  *   flags bit 3: nothing ever arms the barrier the kernel waits on, so the wait runs out: the kernel

@@ -34,7 +34,7 @@ static void load_encode() {
 }
 
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
-                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle_bytes) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return set_error(LOGO_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   if (!aligned16(base) || (row_stride_bytes & 15u))
@@ -44,8 +44,9 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(LOGO_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return LOGO_OK;
 }

@@ -27,11 +27,11 @@ int set_error(int code, const char* fmt, ...);
     if (!(cond)) return ::logo::set_error(code, __VA_ARGS__); \
   } while (0)
 
-// 2-D bf16 tensor map with 128-byte swizzle. `inner` elements are contiguous,
+// 2-D bf16 tensor map with 128-byte (default) or 32-byte swizzle. `inner` elements are contiguous,
 // `outer` rows are `row_stride_bytes` apart. Box = box_inner x box_outer elements;
-// box_inner must be 64 (128 bytes) for the 128-byte swizzle.
+// box_inner must be 64 (128 bytes) for the 128-byte swizzle, 16 (32 bytes) for the 32-byte one.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
-                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle_bytes = 128);
 
 // 2-D fp32 tensor map without swizzle (rows of `box_inner` floats lie contiguously in shared
 // memory): the destination of the bulk reductions that accumulate dQ.

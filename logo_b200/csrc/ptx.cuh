@@ -198,6 +198,20 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// The same for a K-major operand of ONE k-step (16 bf16 = 32 bytes per row) stored with the 32-byte
+// swizzle (rows of 32 bytes, 8-row groups of 256 bytes: SBO = 256; layout type 6). Written by TMA
+// with CU_TENSOR_MAP_SWIZZLE_32B, or by threads when both 16-byte halves of a row hold the same
+// values (the swizzle only exchanges the halves).
+__device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(256 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)6 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 //   a_major / b_major: 0 = K-major, 1 = MN-major.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_major, int b_major) {

@@ -18,14 +18,18 @@ struct SelftestArgs {
 // 128 threads. Shared memory (dynamic, 1024-byte aligned):
 //   [0, 32K)   A: two [128][64] bf16 blocks (columns 0-63, 64-127), 128B-swizzled
 //   [32K, 64K) B: same shape
+//   [64K, 68K) / [68K, 72K): mode 4 only, columns 0-15 of A / of B as [128][16] tiles with the 32-byte swizzle
 __global__ void __launch_bounds__(128, 1)
     umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                         const __grid_constant__ CUtensorMap tm_a32, const __grid_constant__ CUtensorMap tm_b32,
                          const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                          float* __restrict__ c, int* status, SelftestArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + 32768;
+  uint8_t* sA32 = smem + 65536;
+  uint8_t* sB32 = smem + 65536 + 4096;
   __shared__ uint64_t bar_load;
   __shared__ uint64_t bar_mma;
   __shared__ uint32_t tmem_base_slot;
@@ -64,6 +68,7 @@ __global__ void __launch_bounds__(128, 1)
     uint32_t bytes = 0;
     if (!manual_b) bytes += 32768;
     if (a_in_smem && !manual_a) bytes += 32768;
+    if (args.mode == 4) bytes += 8192;
     if (bytes) {
       mbar_arrive_expect_tx(&bar_load, bytes);
     } else {
@@ -76,6 +81,10 @@ __global__ void __launch_bounds__(128, 1)
     if (a_in_smem && !manual_a) {
       tma_load_2d(sA, &tm_a, &bar_load, 0, 0);
       tma_load_2d(sA + 16384, &tm_a, &bar_load, 64, 0);
+    }
+    if (args.mode == 4) {
+      tma_load_2d(sA32, &tm_a32, &bar_load, 0, 0);
+      tma_load_2d(sB32, &tm_b32, &bar_load, 0, 0);
     }
   }
   // thread-written operands: each thread copies its own row, 16 bytes at a time, into the swizzled layout
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(128, 1)
     const uint32_t a_base = smem_u32(sA);
     const uint32_t b_base = smem_u32(sB);
     if (loaded) {
-      if (args.mode == 0) {
+      if (args.mode == 0 || args.mode == 4) {
         const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
 #pragma unroll 1
         for (int kk = 0; kk < 8; ++kk) {
@@ -123,6 +132,8 @@ __global__ void __launch_bounds__(128, 1)
           umma_ss(tmem_d, umma_desc_sw128(a_base + off, args.lbo, 1024), umma_desc_sw128(b_base + off, args.lbo, 1024),
                   idesc, kk > 0);
         }
+        // mode 4: a ninth k-step from the 32-byte-swizzled tiles: D += A[:, 0:16] B[:, 0:16]^T
+        if (args.mode == 4) umma_ss(tmem_d, umma_desc_sw32(smem_u32(sA32)), umma_desc_sw32(smem_u32(sB32)), idesc, true);
       } else if (args.mode == 1) {
         const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 1);
 #pragma unroll 1
@@ -176,17 +187,22 @@ __global__ void __launch_bounds__(128, 1)
 extern "C" int logo_umma_selftest(int mode, int flags, const void* a, const void* b, float* c, uint32_t lbo_bytes,
                                   uint32_t sbo_bytes, uint32_t kstep_bytes, int32_t* status, logo_stream_t stream) {
   using namespace logo;
-  LOGO_REQUIRE(mode >= 0 && mode <= 3, LOGO_ERR_INVALID, "selftest mode must be 0, 1, 2 or 3");
+  LOGO_REQUIRE(mode >= 0 && mode <= 4, LOGO_ERR_INVALID, "selftest mode must be 0 .. 4");
   LOGO_REQUIRE(a && b && c, LOGO_ERR_INVALID, "selftest operands must not be NULL");
   CUtensorMap tm_a, tm_b;
   int rc = make_tmap_2d_bf16(&tm_a, a, 128, 128, 256, 64, 128);
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tm_b, b, 128, 128, 256, 64, 128);
   if (rc) return rc;
-  const int smem_bytes = 65536 + 1024;
+  CUtensorMap tm_a32, tm_b32;
+  rc = make_tmap_2d_bf16(&tm_a32, a, 128, 128, 256, 16, 128, 32);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tm_b32, b, 128, 128, 256, 16, 128, 32);
+  if (rc) return rc;
+  const int smem_bytes = 65536 + 8192 + 1024;
   LOGO_CHECK_CUDA(cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   SelftestArgs args{mode, flags, lbo_bytes, sbo_bytes, kstep_bytes};
-  umma_selftest_kernel<<<1, 128, smem_bytes, (cudaStream_t)stream>>>(tm_a, tm_b, (const __nv_bfloat16*)a,
+  umma_selftest_kernel<<<1, 128, smem_bytes, (cudaStream_t)stream>>>(tm_a, tm_b, tm_a32, tm_b32, (const __nv_bfloat16*)a,
                                                                     (const __nv_bfloat16*)b, c, status, args);
   LOGO_CHECK_CUDA(cudaGetLastError());
   return LOGO_OK;

@@ -211,7 +211,9 @@ def test_umma_operand_encodings(cuda_device):
     b = torch.randn(128, 128, device=cuda_device, generator=g).to(torch.bfloat16)
     abt, ab, atb = a.float() @ b.float().T, a.float() @ b.float(), a.float().T @ b.float()
     # (mode, flags, expected): flags bit 0 / bit 2 = A / B written by threads into the swizzled layout
-    cases = ((0, 0, abt), (0, 1, abt), (1, 0, ab), (1, 4, ab), (1, 5, ab), (2, 0, ab), (3, 0, atb), (3, 4, atb))
+    abt16 = abt + a.float()[:, :16] @ b.float()[:, :16].T   # mode 4: a ninth k-step from 32-byte-swizzled tiles
+    cases = ((0, 0, abt), (0, 1, abt), (1, 0, ab), (1, 4, ab), (1, 5, ab), (2, 0, ab), (3, 0, atb), (3, 4, atb),
+             (4, 0, abt16))
     for mode, flags, ref in cases:
         c = torch.full((128, 128), float("nan"), device=cuda_device)
         st = torch.zeros(1, dtype=torch.int32, device=cuda_device)
