@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(256)
                           const int64_t* __restrict__ q_idx, const int32_t* __restrict__ sq_ptr,
                           __nv_bfloat16* __restrict__ q_sel, __nv_bfloat16* __restrict__ do_sel,
                           float* __restrict__ lse_sel, float* __restrict__ delta_sel, float* __restrict__ dq_acc,
-                          int cap, int n_tokens, int hq, int* status) {
+                          __nv_bfloat16* __restrict__ vec_split, float inv_scale_log2, int cap, int n_tokens, int hq,
+                          int* status) {
   const bool gathered = (q_idx != nullptr);
   const int sq = gathered ? min(max(__ldg(sq_ptr), 0), n_tokens) : n_tokens;
   const int rows_total = gathered ? min(sq + TILE, cap) : sq;
@@ -84,6 +85,23 @@ __global__ void __launch_bounds__(256)
             if ((lane & 15) == 0) {
               delta_sel[(size_t)hh[u] * cap + r] = acc;
               lse_sel[(size_t)hh[u] * cap + r] = lv[u];
+              if (vec_split) {
+                // -lse / c and -delta as three bf16 terms each (24 bits): the single-pass kernel adds them to
+                // its score and dP tiles with a tensor-core k-step
+                const float x = -lv[u] * inv_scale_log2, y = -acc;
+                const __nv_bfloat16 x0 = __float2bfloat16_rn(x);
+                const __nv_bfloat16 x1 = __float2bfloat16_rn(x - __bfloat162float(x0));
+                const __nv_bfloat16 x2 = __float2bfloat16_rn(x - __bfloat162float(x0) - __bfloat162float(x1));
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(y);
+                const __nv_bfloat16 y1 = __float2bfloat16_rn(y - __bfloat162float(y0));
+                const __nv_bfloat16 y2 = __float2bfloat16_rn(y - __bfloat162float(y0) - __bfloat162float(y1));
+                auto pair = [](__nv_bfloat16 lo, __nv_bfloat16 hi) {
+                  return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+                };
+                uint4* dst = reinterpret_cast<uint4*>(vec_split + ((size_t)r * hq + hh[u]) * 16);
+                dst[0] = make_uint4(pair(x0, x1), pair(x2, y0), pair(y1, y2), 0u);
+                dst[1] = make_uint4(0u, 0u, 0u, 0u);
+              }
             }
             if (gathered) {
               const size_t dst = ((size_t)r * hq + hh[u]) * HEAD_DIM + col;
@@ -109,6 +127,11 @@ __global__ void __launch_bounds__(256)
           if ((lane & 15) == 0) {
             delta_sel[(size_t)h1 * cap + r] = 0.f;
             lse_sel[(size_t)h1 * cap + r] = 0.f;
+            if (vec_split) {
+              uint4* dst = reinterpret_cast<uint4*>(vec_split + ((size_t)r * hq + h1) * 16);
+              dst[0] = make_uint4(0u, 0u, 0u, 0u);
+              dst[1] = make_uint4(0u, 0u, 0u, 0u);
+            }
           }
         }
       }
@@ -812,6 +835,7 @@ struct BwdWorkspace {
   float* lse_sel;
   float* delta_sel;
   float* dq_acc;      // [cap][hq][128] fp32 accumulator of the single-pass backward
+  __nv_bfloat16* vec_split;   // [cap][hq][16]: -lse / c and -delta as three bf16 terms each (single-pass backward)
   int cap;
   size_t bytes;
 };
@@ -834,6 +858,7 @@ static BwdWorkspace bwd_workspace_layout(void* base, int n_tokens, int hq, bool 
   w.lse_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
   w.delta_sel = reinterpret_cast<float*>(take((size_t)w.cap * hq * 4));
   w.dq_acc = reinterpret_cast<float*>(take((size_t)w.cap * hq * HEAD_DIM * 4));
+  w.vec_split = reinterpret_cast<__nv_bfloat16*>(take((size_t)w.cap * hq * 16 * 2));
   w.bytes = off;
   return w;
 }
@@ -867,7 +892,8 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   prof_begin(PROF_BWD_PRE, stream);
   bwd_preprocess_kernel<<<sms * 4, 256, 0, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, q_idx, sq_ptr, ws.q_sel,
-      ws.do_sel, ws.lse_sel, ws.delta_sel, fused ? ws.dq_acc : nullptr, ws.cap, n_tokens, hq, status);
+      ws.do_sel, ws.lse_sel, ws.delta_sel, fused ? ws.dq_acc : nullptr, fused ? ws.vec_split : nullptr,
+      1.f / (scale * 1.4426950408889634f), ws.cap, n_tokens, hq, status);
   prof_end(PROF_BWD_PRE, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
 
@@ -909,7 +935,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
 
-  if (fused) return launch_attn_bwd_fused(tm_q, tm_do, tm_k, tm_v, a, ws.dq_acc, sq_ptr, stream);
+  if (fused) return launch_attn_bwd_fused(tm_q, tm_do, tm_k, tm_v, a, ws.dq_acc, ws.vec_split, sq_ptr, stream);
 
   static thread_local int attr_set_dev = -1;
   int dev = 0;

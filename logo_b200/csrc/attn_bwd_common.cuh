@@ -124,6 +124,47 @@ __device__ __forceinline__ void ds_pack_chunk_col(const uint32_t (&p)[32], const
   }
 }
 
+// Variants for score / dP tiles that already carry the row vectors (the single-pass kernel adds
+// -lse / c to S^T and -delta to dP^T on the tensor core): p = 2^(s c), dS = p dp. Positions are only
+// read on masked tiles.
+template <int MASK>
+__device__ __forceinline__ void prob_chunk_biased_t(uint32_t (&r)[32], float c, const int* __restrict__ pos_s, int key_pos,
+                                                    int window) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    int pv4[4] = {0, 0, 0, 0};
+    if (MASK != 0) {
+      const int4 q4 = *reinterpret_cast<const int4*>(pos_s + 4 * g);
+      pv4[0] = q4.x;
+      pv4[1] = q4.y;
+      pv4[2] = q4.z;
+      pv4[3] = q4.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float pv = fast_exp2(__uint_as_float(r[4 * g + e]) * c);
+      if (MASK == 1) pv = (key_pos <= pv4[e]) ? pv : 0.f;
+      if (MASK == 2) pv = (key_pos <= pv4[e] && key_pos >= pv4[e] - window) ? pv : 0.f;
+      r[4 * g + e] = __float_as_uint(pv);
+    }
+  }
+}
+
+__device__ __forceinline__ void prob_chunk_biased(uint32_t (&r)[32], float c, const int* __restrict__ pos_s, bool masked,
+                                                  bool key_valid, int key_pos, int window) {
+  const int kp = key_valid ? key_pos : INT32_MAX;
+  if (!masked) prob_chunk_biased_t<0>(r, c, pos_s, kp, window);
+  else if (window == 0) prob_chunk_biased_t<1>(r, c, pos_s, kp, window);
+  else prob_chunk_biased_t<2>(r, c, pos_s, kp, window);
+}
+
+__device__ __forceinline__ void ds_pack_chunk_biased(const uint32_t (&p)[32], const uint32_t (&dp)[32], uint32_t* pk) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    pk[i] = pack_bf16x2(__uint_as_float(p[2 * i]) * __uint_as_float(dp[2 * i]),
+                        __uint_as_float(p[2 * i + 1]) * __uint_as_float(dp[2 * i + 1]));
+}
+
 __device__ __forceinline__ void pack_chunk(const uint32_t (&p)[32], uint32_t* pk) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(p[2 * i]), __uint_as_float(p[2 * i + 1]));
@@ -171,7 +212,7 @@ __device__ __forceinline__ void dkv_decode_item(const BwdArgs& a, int w, DkvItem
 // (query tile, key tile) pair. dQ is accumulated with fp32 reductions into `dq_acc`
 // ([rows][hq][128], zeroed by the preprocess kernel) and converted by bwd_dq_finish_kernel.
 int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, const CUtensorMap& tm_k,
-                          const CUtensorMap& tm_v, const BwdArgs& a, float* dq_acc, const int32_t* sq_ptr,
-                          cudaStream_t stream);
+                          const CUtensorMap& tm_v, const BwdArgs& a, float* dq_acc, const __nv_bfloat16* vec_split,
+                          const int32_t* sq_ptr, cudaStream_t stream);
 
 }  // namespace logo

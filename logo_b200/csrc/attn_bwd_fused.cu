@@ -4,14 +4,21 @@
 // Work item = (128-key tile, kv head); the CTA keeps the K / V tile in shared memory and the
 // dK / dV accumulators in tensor memory and streams the Q / dO tiles of every query head of
 // the group that can see the key tile. Per step (one query tile):
-//     S^T  = K Q^T            -> TMEM X           (both operands K-major in shared memory)
-//     dP^T = V dO^T           -> TMEM Y
-//     P^T  = exp2(S^T c - lse) masked, bf16       -> written into X (the A operand of dV)
+//     S^T  = K Q^T - lse / c  -> TMEM X           (both operands K-major in shared memory; the row
+//     dP^T = V dO^T - delta   -> TMEM Y            vectors are added by a ninth k-step, see below)
+//     P^T  = exp2(S^T c) masked, bf16             -> written into X (the A operand of dV)
 //     dV  += P^T dO                               (A from TMEM, B = dO tile read MN-major)
-//     dS^T = P^T o (dP^T - delta), bf16           -> written to SHARED memory as a [key][query]
+//     dS^T = P^T o dP^T, bf16                     -> written to SHARED memory as a [key][query]
 //                                                    tile, into the dO stage dV has finished with
 //     dK  += dS^T Q                               (A = the dS^T tile K-major, B = Q tile MN-major)
 //     dQ^T = K^T dS^T         -> TMEM Y           (A = the K tile read MN-major, B = dS^T MN-major)
+// lse and delta are per query row, i.e. per COLUMN of the transposed tiles: every thread of the
+// element-wise warps would need all 64 values of its columns, 16-byte broadcast loads that cost the
+// shared-memory pipe one wavefront per 4 bytes per warp (a quarter of its thread traffic, and the
+// pipe is what bounds this kernel). Instead the preprocess kernel writes -lse / c and -delta of every
+// (row, head) as three bf16 terms each (24 bits) into a [rows][heads][16] array; the tile of a step
+// comes in by TMA with the Q tile (32-byte swizzle) and is the B operand of one more k-step whose A
+// operand is a constant tile of ones in the matching columns: exact products, fp32 sums.
 // dQ^T of the step (rows = head dimension, columns = query rows) is read out of Y by four
 // dedicated warps; each lays its 32 head-dimension columns down as fp32 [query][32] pieces, 32 query
 // rows at a time, in its own double-buffered part of the 32 KB staging tile X and adds them to an
@@ -49,7 +56,11 @@ __device__ __forceinline__ void reg_dec_misc() { asm volatile("setmaxnreg.dec.sy
 // padding): seven 32 KB tiles, then the per-step vectors, barriers and the work-item ring.
 struct FusedSmem {
   static constexpr uint32_t K = 0, V = TILE_BYTES, Q = 2 * TILE_BYTES, DO = 4 * TILE_BYTES, X = 6 * TILE_BYTES;
-  static constexpr uint32_t LSE = 7 * TILE_BYTES, DELTA = LSE + TILE * 4, POS = DELTA + TILE * 4;
+  static constexpr uint32_t X_BYTES = 16384;                 // four read-out warps x two 2 KB buffers
+  static constexpr uint32_t ONES = X + X_BYTES;              // two constant [128][16] A tiles (see VEC)
+  static constexpr uint32_t VEC_BYTES = TILE * 32;           // one [128][16] bf16 tile, 32-byte swizzle
+  static constexpr uint32_t VEC = ONES + 2 * VEC_BYTES;      // 2 stages, loaded with the Q tile
+  static constexpr uint32_t POS = VEC + 2 * VEC_BYTES;
   static constexpr uint32_t BARS = POS + TILE * 4;          // 8-byte aligned
   static constexpr uint32_t N_BARS = 19 + 2 * ITEM_RING;
   static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
@@ -61,17 +72,22 @@ static_assert(FusedSmem::BYTES <= 232448, "the single-pass backward does not fit
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
     attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                          const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
+                          const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_vec,
+                          const BwdArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem + FusedSmem::K;
   uint8_t* sV = smem + FusedSmem::V;
   uint8_t* sQ = smem + FusedSmem::Q;      // 2 stages
   uint8_t* sDO = smem + FusedSmem::DO;    // 2 stages; stage s & 1 holds dS^T of step s once dV(s) is done
-  // X: the two halves of a step's dQ tile ([query][128] fp32) on their way to the bulk reduction; at
-  // the end of an item the staging of the dK / dV stores
+  // X: pieces of a step's dQ tile on their way to the bulk reductions; at the end of an item the
+  // staging of the dK / dV stores
   uint8_t* sX = smem + FusedSmem::X;
-  float* s_lse = reinterpret_cast<float*>(smem + FusedSmem::LSE);
-  float* s_delta = reinterpret_cast<float*>(smem + FusedSmem::DELTA);
+  // -lse / c and -delta of the step's 128 query rows travel as three bf16 terms each in columns 0-2 and
+  // 3-5 of a [128][16] tile (the B operand of a ninth k-step); the matching A tiles hold ones in those
+  // columns for every key row, so the tensor core adds the row vectors to S^T and dP^T (exact products,
+  // fp32 sums) and the element-wise warps never load them.
+  uint8_t* sOnes = smem + FusedSmem::ONES;
+  uint8_t* sVec = smem + FusedSmem::VEC;
   int* s_pos = reinterpret_cast<int*>(smem + FusedSmem::POS);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FusedSmem::BARS);
   uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
@@ -116,6 +132,16 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     tmem_alloc(&tmem_slot, 512);
     tmem_relinquish();
   }
+  if (tid < 2 * TILE) {
+    // tile 0: ones in columns 0-2 (adds -lse / c to S^T), tile 1: ones in columns 3-5 (adds -delta to dP^T).
+    // Both 16-byte halves of a row get the pattern: the 32-byte swizzle only exchanges the halves, and the
+    // second half of the B rows is zero.
+    const uint4 v = (tid < TILE) ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0u, 0x3F800000u, 0x3F803F80u, 0u);
+    uint4* row = reinterpret_cast<uint4*>(sOnes + (tid >> 7) * FusedSmem::VEC_BYTES + (tid & (TILE - 1)) * 32);
+    row[0] = v;
+    row[1] = v;
+    fence_proxy_async_smem();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -136,20 +162,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const float c = a.scale_log2;
     uint32_t idx = 0;
 
-    // lse / delta / pos of row `tid` of query tile `i` of head `hq`: loaded unconditionally from a
-    // clamped row into registers (threads 0-127), stored to the shared vectors between two steps
-    auto fetch_vec = [&](const DkvItem& it, int hq, int i, float& l, float& d, int& p) {
+    // position of row `tid` of query tile `i`: loaded from a clamped row into a register (threads
+    // 0-127), stored to the shared vector between two steps (lse and delta reach the tiles through the
+    // tensor core, see sVec)
+    auto fetch_pos = [&](const DkvItem& it, int i) -> int {
       const int r = i * TILE + (tid & (TILE - 1));
       const int rc = min(r, it.nsel - 1);
-      const size_t sidx = (size_t)hq * a.cap + it.bos_q + rc;
-      l = __ldg(a.lse_sel + sidx);
-      d = __ldg(a.delta_sel + sidx);
-      p = bwd_row_position(a, it.bos_q, rc);
-      if (r >= it.nsel) {   // rows past the end of the sequence see no key
-        l = 0.f;
-        d = 0.f;
-        p = -1;
-      }
+      const int p = bwd_row_position(a, it.bos_q, rc);
+      return r >= it.nsel ? -1 : p;   // rows past the end of the sequence see no key
     };
 
     uint32_t n_ring = 0;
@@ -186,14 +206,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       const bool partial_keys = it.kv_start + TILE > it.len_k;
 
       if (!vec_ready) {
-        if (tid < TILE) {
-          float l, d;
-          int p;
-          fetch_vec(it, it.kvh * G, it.i0, l, d, p);
-          s_lse[tid] = l;
-          s_delta[tid] = d;
-          s_pos[tid] = p;
-        }
+        if (tid < TILE) s_pos[tid] = fetch_pos(it, it.i0);
         named_barrier_sync(3, 256);
       }
 
@@ -209,12 +222,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           w_next = ring_pop(ring, n_ring + 1, it_next, ab);
           vec_next = (w_next >= 0) && (it_next.i_end > it_next.i0);
         }
-        float l_nx = 0.f, d_nx = 0.f;
         int p_nx = -1;
-        if ((has_next || vec_next) && tid < TILE) {
-          if (has_next) fetch_vec(it, it.kvh * G + g_nx, it.i0 + i_nx, l_nx, d_nx, p_nx);
-          else fetch_vec(it_next, it_next.kvh * G, it_next.i0, l_nx, d_nx, p_nx);
-        }
+        if ((has_next || vec_next) && tid < TILE)
+          p_nx = has_next ? fetch_pos(it, it.i0 + i_nx) : fetch_pos(it_next, it_next.i0);
 
         const int pos_first = s_pos[0], pos_last = s_pos[TILE - 1];
         const bool masked = partial_keys || pos_last < 0 || pos_first < it.kv_start + TILE - 1 ||
@@ -225,8 +235,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         tmem_ld32(TM_X + lane_off + (uint32_t)col0, p0);
         tmem_ld32(TM_X + lane_off + (uint32_t)col0 + 32, p1);
         tmem_ld_wait();
-        prob_chunk_col(p0, c, &s_lse[col0], &s_pos[col0], masked, key_valid, key_pos, a.window);
-        prob_chunk_col(p1, c, &s_lse[col0 + 32], &s_pos[col0 + 32], masked, key_valid, key_pos, a.window);
+        // X holds S^T - lse / c: the probabilities are one multiply and one exponential per element
+        prob_chunk_biased(p0, c, &s_pos[col0], masked, key_valid, key_pos, a.window);
+        prob_chunk_biased(p1, c, &s_pos[col0 + 32], masked, key_valid, key_pos, a.window);
         {
           uint32_t pk[32];
           pack_chunk(p0, pk);
@@ -244,13 +255,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           uint32_t d0[32];
           tmem_ld32(TM_Y + lane_off + (uint32_t)col0, d0);
           tmem_ld_wait();
-          ds_pack_chunk_col(p0, d0, &s_delta[col0], ds);
+          ds_pack_chunk_biased(p0, d0, ds);   // Y holds dP^T - delta
         }
         {
           uint32_t d1[32];
           tmem_ld32(TM_Y + lane_off + (uint32_t)col0 + 32, d1);
           tmem_ld_wait();
-          ds_pack_chunk_col(p1, d1, &s_delta[col0 + 32], ds + 16);
+          ds_pack_chunk_biased(p1, d1, ds + 16);
         }
         tc_fence_before();   // Y has been read: after ds_ready the MMA warp may overwrite it with dQ^T
         // dS^T goes into the dO stage of this step as a [key][query] tile (two [128][64] blocks,
@@ -267,11 +278,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         mbar_arrive_warp(&ds_ready);
         // hand the vectors over: every warp has finished reading this step's, then the next step's land
         named_barrier_sync(2, 256);
-        if ((has_next || vec_next) && tid < TILE) {
-          s_lse[tid] = l_nx;
-          s_delta[tid] = d_nx;
-          s_pos[tid] = p_nx;
-        }
+        if ((has_next || vec_next) && tid < TILE) s_pos[tid] = p_nx;
         named_barrier_sync(3, 256);
       }
 
@@ -287,8 +294,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
     // and the 128 query rows of the step as columns. The whole row comes into registers in one round
-    // (Y is released right after it). Every warp then works alone: it owns 8 KB of X as two 4 KB
-    // buffers, writes 32 query rows x its 32 head-dimension columns into one as fp32 [query row][32],
+    // (Y is released right after it). Every warp then works alone: it owns 4 KB of X as two 2 KB
+    // buffers, writes 16 query rows x its 32 head-dimension columns into one as fp32 [query row][32],
     // and its lane 0 sends the buffer to dq_acc with a bulk reduction of its own. A buffer is reused
     // only when the reduction issued two rounds earlier has read it, so the reductions (which drain at
     // about 20 bytes per clock per SM) run under the staging of the following rounds and under the
@@ -296,7 +303,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     reg_dec_dq();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    float* const my_x = reinterpret_cast<float*>(sX + quad * 8192);   // this warp's two [32][32] fp32 buffers
+    float* const my_x = reinterpret_cast<float*>(sX + quad * 4096);   // this warp's two [16][32] fp32 buffers
     uint32_t idx = 0, n_items = 0, n_rounds = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
@@ -323,19 +330,23 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           mbar_arrive_warp(&dq_read);   // Y is free for the next dP^T
           // rows past the last valid query row of the tile hold exact zeros (their dS^T columns are
           // zero); rows past the end of the accumulator are clipped by the tensor map
-          auto send = [&](const uint32_t (&r)[32], int k) {
-            float* buf = my_x + (n_rounds & 1u) * 1024;
-            if (lane == 0) bulk_wait_read_but_one();   // the reduction of two rounds ago has read this buffer
-            __syncwarp();
+          auto send = [&](const uint32_t (&r)[32], int k) {   // query rows 32 k .. 32 k + 31, two pieces of 16
 #pragma unroll
-            for (int j = 0; j < 32; ++j) buf[j * 32 + lane] = __uint_as_float(r[j]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && ok) {
-              tma_reduce_add_2d(&tm_dq, buf, x, y + 32 * k);
-              bulk_commit_group();
+            for (int hf = 0; hf < 2; ++hf) {
+              if (nvalid <= 32 * k + 16 * hf) break;
+              float* buf = my_x + (n_rounds & 1u) * 512;
+              if (lane == 0) bulk_wait_read_but_one();   // the reduction of two rounds ago has read this buffer
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) buf[j * 32 + lane] = __uint_as_float(r[16 * hf + j]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && ok) {
+                tma_reduce_add_2d(&tm_dq, buf, x, y + 32 * k + 16 * hf);
+                bulk_commit_group();
+              }
+              ++n_rounds;
             }
-            ++n_rounds;
           };
           send(r0, 0);
           if (nvalid > 32) send(r1, 1);
@@ -388,6 +399,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_vec);
       uint32_t q_iter = 0, n_items = 0, n_pub = 0;
       DkvItem it, it_ahead;
       long long w_last = -1;
@@ -422,9 +434,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
           const int x = (it.kvh * G + g) * HEAD_DIM, y = it.bos_q + i * TILE;
           mbar_wait(&q_empty[st], ph ^ 1u, ab);
-          mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
+          mbar_arrive_expect_tx(&q_full[st], TILE_BYTES + FusedSmem::VEC_BYTES);
           tma_load_2d(sQ + st * TILE_BYTES, &tm_q, &q_full[st], x, y);
           tma_load_2d(sQ + st * TILE_BYTES + BLK_BYTES, &tm_q, &q_full[st], x + 64, y);
+          tma_load_2d(sVec + st * FusedSmem::VEC_BYTES, &tm_vec, &q_full[st], (it.kvh * G + g) * 16, y);
           mbar_wait(&do_empty[st], ph ^ 1u, ab);
           mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
           tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
@@ -455,9 +468,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
     uint32_t q_iter = 0, n_items = 0;
 
-    auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
+    // S^T = K Q^T - lse / c (ones_tile 0) or dP^T = V dO^T - delta (ones_tile 1): eight k-steps over the
+    // head dimension and a ninth over the [128][16] vector tile of stage `vec_stage`
+    const uint32_t ones_base = smem_u32(sOnes), vec_base = smem_u32(sVec);
+    auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base, uint32_t ones_tile, uint32_t vec_stage) {
       umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
                                    idesc_kk, 0u);
+      umma_ss(d_tmem, umma_desc_sw32(ones_base + ones_tile * FusedSmem::VEC_BYTES),
+              umma_desc_sw32(vec_base + vec_stage * FusedSmem::VEC_BYTES), idesc_kk, 1u);
     };
     auto issue_dv = [&](uint32_t b_base, bool acc) {
       umma_tile_k128<true, true, 2>(TM_DV, TM_X, umma_desc_sw128(b_base, BLK_BYTES, 1024), idesc_mn, acc ? 1u : 0u);
@@ -488,13 +506,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
         mbar_wait(&q_full[st], ph, ab);
         tc_fence_after();
-        issue_kk(TM_X, k_base, q_base + st * TILE_BYTES);
+        issue_kk(TM_X, k_base, q_base + st * TILE_BYTES, 0u, st);
         umma_commit(&st_full);
         mbar_wait(&do_full[st], ph, ab);
         // Y still holds dQ^T of the previous step (of the previous item) until the read-out warps have it
         if (q_iter > 0) mbar_wait(&dq_read, (q_iter - 1u) & 1u, ab);
         tc_fence_after();
-        issue_kk(TM_Y, v_base, do_base + st * TILE_BYTES);
+        issue_kk(TM_Y, v_base, do_base + st * TILE_BYTES, 1u, st);
         umma_commit(&dpt_full);
       }
       for (int s = 0; s < n_steps; ++s, ++q_iter) {
@@ -510,7 +528,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         if (has_next) {
           mbar_wait(&q_full[st_n], ph_n, ab);
           tc_fence_after();
-          issue_kk(TM_X, k_base, q_base + st_n * TILE_BYTES);
+          issue_kk(TM_X, k_base, q_base + st_n * TILE_BYTES, 0u, st_n);
           umma_commit(&st_full);
         }
         mbar_wait(&ds_ready, q_iter & 1u, ab);
@@ -526,7 +544,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           mbar_wait(&do_full[st_n], ph_n, ab);
           mbar_wait(&dq_read, q_iter & 1u, ab);
           tc_fence_after();
-          issue_kk(TM_Y, v_base, do_base + st_n * TILE_BYTES);
+          issue_kk(TM_Y, v_base, do_base + st_n * TILE_BYTES, 1u, st_n);
           umma_commit(&dpt_full);
         }
       }
@@ -566,8 +584,8 @@ __global__ void __launch_bounds__(256)
 }
 
 int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, const CUtensorMap& tm_k,
-                          const CUtensorMap& tm_v, const BwdArgs& a, float* dq_acc, const int32_t* sq_ptr,
-                          cudaStream_t stream) {
+                          const CUtensorMap& tm_v, const BwdArgs& a, float* dq_acc, const __nv_bfloat16* vec_split,
+                          const int32_t* sq_ptr, cudaStream_t stream) {
   static thread_local int attr_set_dev = -1;
   int dev = 0;
   LOGO_CHECK_CUDA(cudaGetDevice(&dev));
@@ -581,11 +599,13 @@ int launch_attn_bwd_fused(const CUtensorMap& tm_q, const CUtensorMap& tm_do, con
   prof_begin(PROF_BWD_FUSED, stream);
   CUtensorMap tm_dq;
   const uint64_t acc_rows = a.q_idx ? (uint64_t)a.cap : (uint64_t)a.n_tokens;
-  // one reduction = 32 query rows x 32 head-dimension columns (a 128-byte piece of each row)
-  const int rc = make_tmap_2d_f32(&tm_dq, dq_acc, (uint64_t)a.hq * HEAD_DIM, acc_rows, (uint64_t)a.hq * HEAD_DIM * 4,
-                                  32, 32);
+  // one reduction = 16 query rows x 32 head-dimension columns (a 128-byte piece of each row)
+  int rc = make_tmap_2d_f32(&tm_dq, dq_acc, (uint64_t)a.hq * HEAD_DIM, acc_rows, (uint64_t)a.hq * HEAD_DIM * 4, 32, 16);
   if (rc) return rc;
-  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, FusedSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, a);
+  CUtensorMap tm_vec;   // [rows][hq][16] bf16: the split -lse / c and -delta of every (row, head)
+  rc = make_tmap_2d_bf16(&tm_vec, vec_split, (uint64_t)a.hq * 16, acc_rows, (uint64_t)a.hq * 32, 16, TILE, 32);
+  if (rc) return rc;
+  attn_bwd_fused_kernel<<<sms, FUSED_THREADS, FusedSmem::BYTES, stream>>>(tm_q, tm_do, tm_k, tm_v, tm_dq, tm_vec, a);
   prof_end(PROF_BWD_FUSED, stream);
   LOGO_CHECK_CUDA(cudaGetLastError());
   prof_begin(PROF_BWD_FINISH, stream);
