@@ -695,14 +695,19 @@ def leg_layer(ctx, steps, warmup):
             work.wait()
 
     ms = _timed(step, steps, warmup, ctx)
+    ms_sync = None
+    if world > 1:
+        # the first timed block also pays NCCL's one-off set-up for this gather: time the overlapped form
+        # again after the other one and keep the better of its two measurements
+        ms_sync = _timed(lambda: step(False), steps, warmup, ctx)
+        ms = min(ms, _timed(step, steps, warmup, ctx))
     res = {"tokens": N_TOK, "sequence_lengths": lens, "tokens_per_rank": rows, "partition": "whole sequences, "
            "longest estimated cost first", "collective": "all_gather of the layer outputs (un-padded), overlapped "
            "with the backward" if world > 1 else None,
            "ms_per_step": ms / steps, "tokens_per_s": N_TOK * steps / (ms * 1e-3),
            "note": "a sequence is never split: with 8 ranks each holds one, and the longest (6286 of 32768 tokens) "
                    "sets the step time"}
-    if world > 1:
-        ms_sync = _timed(lambda: step(False), steps, warmup, ctx)
+    if ms_sync is not None:
         res["ms_per_step_gather_not_overlapped"] = ms_sync / steps
     del layer
     return res
