@@ -365,6 +365,9 @@ int logo_profile_read(double* total_ms, int* launches, int n);
  *   mode 3: C = A^T * B   (both operands MN-major: rows of a and b are the reduction index)
  *   mode 4: C = A * B^T + A[:, 0:16] * B[:, 0:16]^T   (mode 0 plus a ninth k-step whose [128][16]
  *           operand tiles use the 32-byte swizzle)
+ *   mode 5: C = A * B^T + 1 x (a[0, 0:16] . B[:, 0:16]^T)   (the ninth k-step's A operand is a 256-byte
+ *           tile of identical rows without swizzle; kstep_bytes / sbo_bytes are its distances between
+ *           K chunks / 8-row groups: 128 / 0)
  *   a, b: bf16 [128][128] row-major; c: fp32 [128][128]
  *   flags bit 0 / bit 2: stage A / B through thread-written swizzled shared memory instead of TMA.
  *   flags bit 3: nothing ever arms the barrier the kernel waits on, so the wait runs out: the kernel

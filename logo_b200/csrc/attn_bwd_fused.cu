@@ -56,11 +56,12 @@ __device__ __forceinline__ void reg_dec_misc() { asm volatile("setmaxnreg.dec.sy
 // padding): seven 32 KB tiles, then the per-step vectors, barriers and the work-item ring.
 struct FusedSmem {
   static constexpr uint32_t K = 0, V = TILE_BYTES, Q = 2 * TILE_BYTES, DO = 4 * TILE_BYTES, X = 6 * TILE_BYTES;
-  static constexpr uint32_t X_BYTES = 16384;                 // four read-out warps x two 2 KB buffers
-  static constexpr uint32_t ONES = X + X_BYTES;              // two constant [128][16] A tiles (see VEC)
+  static constexpr uint32_t X_BYTES = 24576;                 // four read-out warps x three 2 KB buffers
   static constexpr uint32_t VEC_BYTES = TILE * 32;           // one [128][16] bf16 tile, 32-byte swizzle
-  static constexpr uint32_t VEC = ONES + 2 * VEC_BYTES;      // 2 stages, loaded with the Q tile
-  static constexpr uint32_t POS = VEC + 2 * VEC_BYTES;
+  static constexpr uint32_t VEC = X + X_BYTES;               // 2 stages, loaded with the Q tile
+  static constexpr uint32_t ONES_BYTES = 256;                // a [128][16] tile of identical rows (see sOnes)
+  static constexpr uint32_t ONES = VEC + 2 * VEC_BYTES;      // two of them
+  static constexpr uint32_t POS = ONES + 2 * ONES_BYTES;
   static constexpr uint32_t BARS = POS + TILE * 4;          // 8-byte aligned
   static constexpr uint32_t N_BARS = 19 + 2 * ITEM_RING;
   static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
@@ -85,7 +86,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   // -lse / c and -delta of the step's 128 query rows travel as three bf16 terms each in columns 0-2 and
   // 3-5 of a [128][16] tile (the B operand of a ninth k-step); the matching A tiles hold ones in those
   // columns for every key row, so the tensor core adds the row vectors to S^T and dP^T (exact products,
-  // fp32 sums) and the element-wise warps never load them.
+  // fp32 sums) and the element-wise warps never load them. All rows of an A tile being equal, it is
+  // stored as two 128-byte core matrices without swizzle and a zero distance between 8-row groups.
   uint8_t* sOnes = smem + FusedSmem::ONES;
   uint8_t* sVec = smem + FusedSmem::VEC;
   int* s_pos = reinterpret_cast<int*>(smem + FusedSmem::POS);
@@ -132,14 +134,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     tmem_alloc(&tmem_slot, 512);
     tmem_relinquish();
   }
-  if (tid < 2 * TILE) {
-    // tile 0: ones in columns 0-2 (adds -lse / c to S^T), tile 1: ones in columns 3-5 (adds -delta to dP^T).
-    // Both 16-byte halves of a row get the pattern: the 32-byte swizzle only exchanges the halves, and the
-    // second half of the B rows is zero.
-    const uint4 v = (tid < TILE) ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0u, 0x3F800000u, 0x3F803F80u, 0u);
-    uint4* row = reinterpret_cast<uint4*>(sOnes + (tid >> 7) * FusedSmem::VEC_BYTES + (tid & (TILE - 1)) * 32);
-    row[0] = v;
-    row[1] = v;
+  if (tid < 32) {
+    // tile 0: ones in columns 0-2 (adds -lse / c to S^T), tile 1: ones in columns 3-5 (adds -delta to dP^T);
+    // per tile 8 rows x 16 bytes for columns 0-7, then 8 rows of zeros for columns 8-15
+    const int tile = tid >> 4, r = tid & 15;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < 8) v = tile == 0 ? make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u) : make_uint4(0u, 0x3F800000u, 0x3F803F80u, 0u);
+    reinterpret_cast<uint4*>(sOnes + tile * FusedSmem::ONES_BYTES)[r] = v;
     fence_proxy_async_smem();
   }
   tc_fence_before();
@@ -294,17 +295,17 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     // ================= dQ read-out warps =================
     // Lane l of the warp of quarter q holds row 32 q + l of dQ^T (one element of the head dimension)
     // and the 128 query rows of the step as columns. The whole row comes into registers in one round
-    // (Y is released right after it). Every warp then works alone: it owns 4 KB of X as two 2 KB
+    // (Y is released right after it). Every warp then works alone: it owns 6 KB of X as three 2 KB
     // buffers, writes 16 query rows x its 32 head-dimension columns into one as fp32 [query row][32],
     // and its lane 0 sends the buffer to dq_acc with a bulk reduction of its own. A buffer is reused
-    // only when the reduction issued two rounds earlier has read it, so the reductions (which drain at
+    // only when the reduction issued three rounds earlier has read it, so the reductions (which drain at
     // about 20 bytes per clock per SM) run under the staging of the following rounds and under the
     // next step instead of being waited for one by one.
     reg_dec_dq();
     const int quad = warp & 3;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    float* const my_x = reinterpret_cast<float*>(sX + quad * 4096);   // this warp's two [16][32] fp32 buffers
-    uint32_t idx = 0, n_items = 0, n_rounds = 0;
+    float* const my_x = reinterpret_cast<float*>(sX + quad * 6144);   // this warp's three [16][32] fp32 buffers
+    uint32_t idx = 0, n_items = 0, buf_no = 0;
     for (uint32_t n_ring = 0;; ++n_ring) {
       DkvItem it;
       const long long w = ring_pop(ring, n_ring, it, ab);
@@ -334,8 +335,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
               if (nvalid <= 32 * k + 16 * hf) break;
-              float* buf = my_x + (n_rounds & 1u) * 512;
-              if (lane == 0) bulk_wait_read_but_one();   // the reduction of two rounds ago has read this buffer
+              float* buf = my_x + buf_no * 512;
+              if (lane == 0) bulk_wait_read_but_two();   // the reduction of three rounds ago has read this buffer
               __syncwarp();
 #pragma unroll
               for (int j = 0; j < 16; ++j) buf[j * 32 + lane] = __uint_as_float(r[16 * hf + j]);
@@ -345,7 +346,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
                 tma_reduce_add_2d(&tm_dq, buf, x, y + 32 * k + 16 * hf);
                 bulk_commit_group();
               }
-              ++n_rounds;
+              buf_no = buf_no == 2u ? 0u : buf_no + 1u;
             }
           };
           send(r0, 0);
@@ -474,7 +475,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
     auto issue_kk = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base, uint32_t ones_tile, uint32_t vec_stage) {
       umma_tile_k128<false, false>(d_tmem, umma_desc_sw128(a_base, 0, 1024), umma_desc_sw128(b_base, 0, 1024),
                                    idesc_kk, 0u);
-      umma_ss(d_tmem, umma_desc_sw32(ones_base + ones_tile * FusedSmem::VEC_BYTES),
+      umma_ss(d_tmem, umma_desc_noswizzle(ones_base + ones_tile * FusedSmem::ONES_BYTES, 128, 0),
               umma_desc_sw32(vec_base + vec_stage * FusedSmem::VEC_BYTES), idesc_kk, 1u);
     };
     auto issue_dv = [&](uint32_t b_base, bool acc) {

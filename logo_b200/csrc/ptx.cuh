@@ -146,6 +146,8 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // all but the newest bulk group of this thread have finished reading their shared-memory source
 __device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// ... all but the two newest
+__device__ __forceinline__ void bulk_wait_read_but_two() { asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); }
 // every bulk group of this thread has completed (its global writes are performed)
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -209,6 +211,18 @@ __device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t saddr) {
   d |= (uint64_t)(256 >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)6 << 61;
+  return d;
+}
+
+// The same without swizzle (layout type 0): 8-row x 16-byte core matrices of 128 contiguous bytes; for a
+// K-major operand `lbo_bytes` is the distance between the core matrices of consecutive 16-byte K chunks
+// and `sbo_bytes` the distance between consecutive 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
   return d;
 }
 

@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(128, 1)
     if (!manual_b) bytes += 32768;
     if (a_in_smem && !manual_a) bytes += 32768;
     if (args.mode == 4) bytes += 8192;
+    if (args.mode == 5) bytes += 4096;
     if (bytes) {
       mbar_arrive_expect_tx(&bar_load, bytes);
     } else {
@@ -86,6 +87,14 @@ __global__ void __launch_bounds__(128, 1)
       tma_load_2d(sA32, &tm_a32, &bar_load, 0, 0);
       tma_load_2d(sB32, &tm_b32, &bar_load, 0, 0);
     }
+    if (args.mode == 5) tma_load_2d(sB32, &tm_b32, &bar_load, 0, 0);
+  }
+  if (args.mode == 5 && tid < 16) {
+    // two core matrices (8 rows x 16 bytes each) whose rows all hold a[0][0:8] / a[0][8:16]: with a zero
+    // distance between 8-row groups the 256 bytes stand for a [128][16] tile of identical rows
+    const uint4* src = reinterpret_cast<const uint4*>(a);
+    reinterpret_cast<uint4*>(sA32)[tid] = src[tid >> 3];
+    fence_proxy_async_smem();
   }
   // thread-written operands: each thread copies its own row, 16 bytes at a time, into the swizzled layout
   auto copy_row = [&](const __nv_bfloat16* src_mat, uint8_t* dst) {
@@ -124,7 +133,7 @@ __global__ void __launch_bounds__(128, 1)
     const uint32_t a_base = smem_u32(sA);
     const uint32_t b_base = smem_u32(sB);
     if (loaded) {
-      if (args.mode == 0 || args.mode == 4) {
+      if (args.mode == 0 || args.mode == 4 || args.mode == 5) {
         const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
 #pragma unroll 1
         for (int kk = 0; kk < 8; ++kk) {
@@ -134,6 +143,10 @@ __global__ void __launch_bounds__(128, 1)
         }
         // mode 4: a ninth k-step from the 32-byte-swizzled tiles: D += A[:, 0:16] B[:, 0:16]^T
         if (args.mode == 4) umma_ss(tmem_d, umma_desc_sw32(smem_u32(sA32)), umma_desc_sw32(smem_u32(sB32)), idesc, true);
+        // mode 5: the ninth k-step's A operand is the 256-byte tile of identical rows, without swizzle
+        // (lbo / sbo of the call describe it): D += ones x (a[0][0:16] . B[:, 0:16]^T)
+        if (args.mode == 5)
+          umma_ss(tmem_d, umma_desc_noswizzle(smem_u32(sA32), args.kstep, args.sbo), umma_desc_sw32(smem_u32(sB32)), idesc, true);
       } else if (args.mode == 1) {
         const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 1);
 #pragma unroll 1
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(128, 1)
 extern "C" int logo_umma_selftest(int mode, int flags, const void* a, const void* b, float* c, uint32_t lbo_bytes,
                                   uint32_t sbo_bytes, uint32_t kstep_bytes, int32_t* status, logo_stream_t stream) {
   using namespace logo;
-  LOGO_REQUIRE(mode >= 0 && mode <= 4, LOGO_ERR_INVALID, "selftest mode must be 0 .. 4");
+  LOGO_REQUIRE(mode >= 0 && mode <= 5, LOGO_ERR_INVALID, "selftest mode must be 0 .. 5");
   LOGO_REQUIRE(a && b && c, LOGO_ERR_INVALID, "selftest operands must not be NULL");
   CUtensorMap tm_a, tm_b;
   int rc = make_tmap_2d_bf16(&tm_a, a, 128, 128, 256, 64, 128);

@@ -212,13 +212,17 @@ def test_umma_operand_encodings(cuda_device):
     abt, ab, atb = a.float() @ b.float().T, a.float() @ b.float(), a.float().T @ b.float()
     # (mode, flags, expected): flags bit 0 / bit 2 = A / B written by threads into the swizzled layout
     abt16 = abt + a.float()[:, :16] @ b.float()[:, :16].T   # mode 4: a ninth k-step from 32-byte-swizzled tiles
+    # mode 5: the ninth k-step's A operand is a 256-byte tile of identical rows (a[0, 0:16]), no swizzle,
+    # distance 128 bytes between its two K chunks and 0 between 8-row groups
+    abt_row = abt + (b.float()[:, :16] @ a.float()[0, :16])[None, :]
     cases = ((0, 0, abt), (0, 1, abt), (1, 0, ab), (1, 4, ab), (1, 5, ab), (2, 0, ab), (3, 0, atb), (3, 4, atb),
-             (4, 0, abt16))
+             (4, 0, abt16), (5, 0, abt_row))
     for mode, flags, ref in cases:
         c = torch.full((128, 128), float("nan"), device=cuda_device)
         st = torch.zeros(1, dtype=torch.int32, device=cuda_device)
-        rc = lib.logo_umma_selftest(mode, flags, a.data_ptr(), b.data_ptr(), c.data_ptr(), 16384 if mode else 0, 1024,
-                                    2048, st.data_ptr(), None)
+        lbo, sbo, kstep = (0, 0, 128) if mode == 5 else (16384 if mode else 0, 1024, 2048)
+        rc = lib.logo_umma_selftest(mode, flags, a.data_ptr(), b.data_ptr(), c.data_ptr(), lbo, sbo, kstep,
+                                    st.data_ptr(), None)
         _lib.check(rc, "logo_umma_selftest")
         torch.cuda.synchronize()
         assert int(st.item()) == 0
