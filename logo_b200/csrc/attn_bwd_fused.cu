@@ -534,11 +534,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         }
         mbar_wait(&ds_ready, q_iter & 1u, ab);
         tc_fence_after();
+        // dK first: it is the last reader of the Q stage, whose refill (two steps ahead) is what the next
+        // but one S^T waits for; the read-out warps have slack for the 512 clocks dQ^T comes later
+        issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
+        umma_commit(&q_empty[st]);   // the Q tile of this stage may be refilled
         issue_dq(do_base + st * TILE_BYTES);
         umma_commit(&dq_full);
-        issue_dk(do_base + st * TILE_BYTES, q_base + st * TILE_BYTES, s > 0);
-        umma_commit(&q_empty[st]);   // Q and dS^T of this stage have been consumed: both tiles may be refilled
-        umma_commit(&do_empty[st]);
+        umma_commit(&do_empty[st]);  // dS^T (in the dO stage) has been consumed too
         // every product that reads K / V has been issued: the next item's tiles may come in
         if (!has_next) umma_commit(&kv_free);
         if (has_next) {
