@@ -177,8 +177,8 @@ int logo_swa_fwd(const void* q, const void* k, const void* v, void* o, float* ls
  *   dk, dv [n_tokens, h, 128] bf16: fully written
  *   workspace: logo_attn_bwd_workspace_bytes(n_tokens, hq, gathered) bytes, 256-byte aligned;
  *              gathered = 1 for logo_sq_attn_bwd (packed copies of the selected Q / dO rows,
- *              head-major lse and delta, fp32 dQ accumulator), 0 for logo_swa_bwd (lse, delta and
- *              the accumulator)
+ *              head-major lse and delta, fp32 dQ accumulator, the per-row lse / delta terms the single
+ *              pass feeds to the tensor core), 0 for logo_swa_bwd (the same without the packed copies)
  *
  * Two implementations exist per branch (0 = global / logo_sq_attn_bwd, 1 = local / logo_swa_bwd),
  * chosen process-wide with logo_set_backward_mode(branch, mode):
