@@ -37,6 +37,7 @@ constexpr int FWD_THREADS = (FWD_SM_WARPS + 4) * 32;   // + producer, MMA issuer
 constexpr int FWD_STAGES = 2;
 constexpr int FWD_SMEM_BYTES = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr int FWD_MAX_ORDERED_SEQ = 16;    // up to this many sequences the work list is ordered by cost across sequences
 
 struct FwdItem {
   int hq, kvh, bos_q, bos_k, row0;
@@ -45,11 +46,49 @@ struct FwdItem {
 };
 
 __device__ __forceinline__ void fwd_decode_item(const AttnArgs& a, int w, int total_pairs, FwdItem& it) {
-  const int pair_g = total_pairs - 1 - w / a.hq;
   it.hq = w % a.hq;
   it.kvh = it.hq / (a.hq / a.h);
-  const int seq = find_sequence(a.tile_off, a.n_seq, pair_g);
-  const int pair_l = pair_g - __ldg(a.tile_off + seq);
+  int seq, pair_l;
+  if (a.n_seq <= FWD_MAX_ORDERED_SEQ) {
+    // Heaviest first over ALL sequences: the cost of a pair grows with its index p inside its sequence, so
+    // the list goes by p, highest first, taking pair p of every sequence that has one (walking the sequences
+    // one after the other would leave the heavy pairs of the last-walked sequence for the end of the
+    // launch). g(L) = sum over sequences of max(pairs - L, 0) is the number of items with p >= L.
+    const int k = w / a.hq;
+    int np[FWD_MAX_ORDERED_SEQ];
+    int max_np = 0;
+#pragma unroll
+    for (int s = 0; s < FWD_MAX_ORDERED_SEQ; ++s) {
+      np[s] = s < a.n_seq ? __ldg(a.tile_off + s + 1) - __ldg(a.tile_off + s) : 0;
+      max_np = max(max_np, np[s]);
+    }
+    auto at_or_above = [&](int L) {
+      int g = 0;
+#pragma unroll
+      for (int s = 0; s < FWD_MAX_ORDERED_SEQ; ++s) g += max(np[s] - L, 0);
+      return g;
+    };
+    int lo = 0, hi = max(max_np - 1, 0);   // smallest L with at_or_above(L + 1) <= k: the level of item k
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (at_or_above(mid + 1) <= k) hi = mid; else lo = mid + 1;
+    }
+    const int j = k - at_or_above(lo + 1);   // the j-th sequence with more than `lo` pairs
+    seq = 0;
+    int c = 0;
+#pragma unroll
+    for (int s = 0; s < FWD_MAX_ORDERED_SEQ; ++s) {
+      if (np[s] > lo) {
+        if (c == j) seq = s;
+        ++c;
+      }
+    }
+    pair_l = min(lo, max(np[seq] - 1, 0));
+  } else {
+    const int pair_g = total_pairs - 1 - w / a.hq;
+    seq = find_sequence(a.tile_off, a.n_seq, pair_g);
+    pair_l = pair_g - __ldg(a.tile_off + seq);
+  }
   it.bos_q = __ldg(a.cu_q + seq);
   const int nsel = __ldg(a.cu_q + seq + 1) - it.bos_q;
   it.bos_k = __ldg(a.cu_k + seq);
