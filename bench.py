@@ -392,7 +392,7 @@ def run_gpu(args):
         "bwd_dq": 1.5 * f_fwd / (kernel_ms["bwd_dq"] * 1e-3) / 1e12 if kernel_ms["bwd_dq"] else None,
     }
 
-    # the other ratios of the configuration's sweep (same step, 5 timed steps each; not the headline)
+    # the other ratios of the configuration's sweep (same step, 20 timed steps each; not the headline)
     sweep = {f"{args.ratio:g}": round(value / world, 1)}
     if not args.skip_e2e:
         for r in (0.125, 0.25, 0.5, 1.0):
@@ -412,16 +412,16 @@ def run_gpu(args):
                     run2 = g2.replay
                 except Exception:   # noqa: BLE001
                     pass
-            for _ in range(3):
+            for _ in range(10):
                 run2()
             torch.cuda.synchronize()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s0.record()
-            for _ in range(5):
+            for _ in range(20):
                 run2()
             s1.record()
             torch.cuda.synchronize()
-            sweep[f"{r:g}"] = round(f2 * 5 / (s0.elapsed_time(s1) * 1e-3) / 1e12, 1)
+            sweep[f"{r:g}"] = round(f2 * 20 / (s0.elapsed_time(s1) * 1e-3) / 1e12, 1)
             del b2
 
     if args.skip_cpu:
