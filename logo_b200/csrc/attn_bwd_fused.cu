@@ -63,7 +63,7 @@ struct FusedSmem {
   static constexpr uint32_t ONES = VEC + 2 * VEC_BYTES;      // two of them
   static constexpr uint32_t POS = ONES + 2 * ONES_BYTES;
   static constexpr uint32_t BARS = POS + TILE * 4;          // 8-byte aligned
-  static constexpr uint32_t N_BARS = 19 + 2 * ITEM_RING;
+  static constexpr uint32_t N_BARS = 21 + 2 * ITEM_RING;
   static constexpr uint32_t ITEMS = BARS + N_BARS * 8;
   static constexpr uint32_t MISC = ITEMS + ITEM_RING * ITEM_WORDS * 4;   // tmem slot, abort flag
   static constexpr uint32_t BYTES = MISC + 16;
@@ -92,10 +92,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
   uint8_t* sVec = smem + FusedSmem::VEC;
   int* s_pos = reinterpret_cast<int*>(smem + FusedSmem::POS);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FusedSmem::BARS);
-  uint64_t &kv_full = bars[0], &kv_free = bars[1], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
+  uint64_t &k_full = bars[0], &k_free = bars[1], &v_full = bars[19], &v_free = bars[20], *q_full = bars + 2, *q_empty = bars + 4, *do_full = bars + 6,
            *do_empty = bars + 8, &st_full = bars[10], &dpt_full = bars[11], &p_ready = bars[12], &ds_ready = bars[13],
            &dq_full = bars[14], &dv_done = bars[15], &dq_read = bars[16], &acc_read = bars[17], &acc_done = bars[18];
-  const ItemRing ring{reinterpret_cast<int*>(smem + FusedSmem::ITEMS), bars + 19, bars + 19 + ITEM_RING};
+  const ItemRing ring{reinterpret_cast<int*>(smem + FusedSmem::ITEMS), bars + 21, bars + 21 + ITEM_RING};
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + FusedSmem::MISC);
   int& abort_flag = *reinterpret_cast<int*>(smem + FusedSmem::MISC + 4);
 
@@ -110,8 +110,10 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
 
   if (tid == 0) {
     abort_flag = 0;
-    mbar_init(&kv_full, 1);
-    mbar_init(&kv_free, 1);
+    mbar_init(&k_full, 1);
+    mbar_init(&k_free, 1);
+    mbar_init(&v_full, 1);
+    mbar_init(&v_free, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
@@ -414,20 +416,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
       bool have = next_item(it);
       while (have) {
         const int nq = max(it.i_end - it.i0, 0);
-        if (nq > 0) {
-          const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
-          mbar_wait(&kv_free, (n_items & 1u) ^ 1u, ab);
-          mbar_arrive_expect_tx(&kv_full, 2 * TILE_BYTES);
-          tma_load_2d(sK, &tm_k, &kv_full, xk, yk);
-          tma_load_2d(sK + BLK_BYTES, &tm_k, &kv_full, xk + 64, yk);
-          tma_load_2d(sV, &tm_v, &kv_full, xk, yk);
-          tma_load_2d(sV + BLK_BYTES, &tm_v, &kv_full, xk + 64, yk);
-          ++n_items;
-        }
-        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
-        bool have_ahead = ahead ? next_item(it_ahead) : false;
         int g = 0, i = it.i0;   // query head of the group, query tile
-        for (int s = 0; s < nq * G; ++s, ++q_iter, ++i) {
+        auto load_step = [&]() {   // the Q (+ row-vector) and dO tiles of the next step of this item
           if (i == it.i_end) {
             i = it.i0;
             ++g;
@@ -443,7 +433,28 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
           mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
           tma_load_2d(sDO + st * TILE_BYTES, &tm_do, &do_full[st], x, y);
           tma_load_2d(sDO + st * TILE_BYTES + BLK_BYTES, &tm_do, &do_full[st], x + 64, y);
+          ++q_iter;
+          ++i;
+        };
+        if (nq > 0) {
+          // K and V are single-buffered. V is last read by the item's last dP^T, issued a whole step before
+          // the item ends, so the next V tile comes in under that step; then the first Q / dO tiles (their
+          // stages are free); only the K tile has to wait for the item's last product.
+          const int xk = it.kvh * HEAD_DIM, yk = it.bos_k + it.kv_start;
+          mbar_wait(&v_free, (n_items & 1u) ^ 1u, ab);
+          mbar_arrive_expect_tx(&v_full, TILE_BYTES);
+          tma_load_2d(sV, &tm_v, &v_full, xk, yk);
+          tma_load_2d(sV + BLK_BYTES, &tm_v, &v_full, xk + 64, yk);
+          load_step();
+          mbar_wait(&k_free, (n_items & 1u) ^ 1u, ab);
+          mbar_arrive_expect_tx(&k_full, TILE_BYTES);
+          tma_load_2d(sK, &tm_k, &k_full, xk, yk);
+          tma_load_2d(sK + BLK_BYTES, &tm_k, &k_full, xk + 64, yk);
+          ++n_items;
         }
+        const bool ahead = (total_items - w_last) > 6ll * gridDim.x;
+        bool have_ahead = ahead ? next_item(it_ahead) : false;
+        for (int s = 1; s < nq * G; ++s) load_step();
         if (!ahead) have_ahead = next_item(it_ahead);
         it = it_ahead;
         have = have_ahead;
@@ -500,21 +511,22 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         continue;
       }
       const int n_steps = nq * G;
-      mbar_wait(&kv_full, n_items & 1u, ab);
-      ++n_items;
-      tc_fence_after();
       {
         const uint32_t st = q_iter & 1u, ph = (q_iter >> 1) & 1u;
+        mbar_wait(&k_full, n_items & 1u, ab);
         mbar_wait(&q_full[st], ph, ab);
         tc_fence_after();
         issue_kk(TM_X, k_base, q_base + st * TILE_BYTES, 0u, st);
         umma_commit(&st_full);
+        mbar_wait(&v_full, n_items & 1u, ab);
         mbar_wait(&do_full[st], ph, ab);
         // Y still holds dQ^T of the previous step (of the previous item) until the read-out warps have it
         if (q_iter > 0) mbar_wait(&dq_read, (q_iter - 1u) & 1u, ab);
         tc_fence_after();
         issue_kk(TM_Y, v_base, do_base + st * TILE_BYTES, 1u, st);
         umma_commit(&dpt_full);
+        if (n_steps == 1) umma_commit(&v_free);   // no other product of this item reads V
+        ++n_items;
       }
       for (int s = 0; s < n_steps; ++s, ++q_iter) {
         const uint32_t st = q_iter & 1u;
@@ -541,14 +553,15 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1)
         issue_dq(do_base + st * TILE_BYTES);
         umma_commit(&dq_full);
         umma_commit(&do_empty[st]);  // dS^T (in the dO stage) has been consumed too
-        // every product that reads K / V has been issued: the next item's tiles may come in
-        if (!has_next) umma_commit(&kv_free);
+        // every product that reads K has been issued: the next item's K tile may come in
+        if (!has_next) umma_commit(&k_free);
         if (has_next) {
           mbar_wait(&do_full[st_n], ph_n, ab);
           mbar_wait(&dq_read, q_iter & 1u, ab);
           tc_fence_after();
           issue_kk(TM_Y, v_base, do_base + st_n * TILE_BYTES, 1u, st_n);
           umma_commit(&dpt_full);
+          if (s + 2 == n_steps) umma_commit(&v_free);   // that was the item's last dP^T: V may be replaced
         }
       }
       umma_commit(&acc_done);
